@@ -1,0 +1,381 @@
+// C ABI of the codecs: argument checking, geometry, launches.
+// Declarations and the reference interfaces they replace: include/cswap_b200.h,
+// include/cswap_compat.h.
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/cswap_b200.h"
+#include "../../include/cswap_compat.h"
+#include "internal.h"
+#include "sparse_kernels.h"
+#include "zfp_kernels.h"
+
+namespace csw {
+
+thread_local int tl_cuda_error = 0;
+
+csw_status cuda_fail(cudaError_t e) {
+  tl_cuda_error = (int)e;
+  return CSW_ERR_CUDA;
+}
+
+// ---- per-device state: SM count and the device status word ----------------------
+namespace {
+struct DeviceState {
+  bool ready = false;
+  int sm_count = 0;
+  int* d_status = nullptr;  // one int, zero when healthy
+};
+constexpr int kMaxDevices = 64;
+DeviceState g_dev[kMaxDevices];
+std::mutex g_dev_mu;
+}  // namespace
+
+csw_status device_state(int* sm_count, int** d_status) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (dev < 0 || dev >= kMaxDevices) return CSW_ERR_ARG;
+  std::lock_guard<std::mutex> lk(g_dev_mu);
+  DeviceState& s = g_dev[dev];
+  if (!s.ready) {
+    e = cudaDeviceGetAttribute(&s.sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return cuda_fail(e);
+    e = cudaMalloc(&s.d_status, sizeof(int));
+    if (e != cudaSuccess) return cuda_fail(e);
+    e = cudaMemset(s.d_status, 0, sizeof(int));
+    if (e != cudaSuccess) return cuda_fail(e);
+    s.ready = true;
+  }
+  if (sm_count) *sm_count = s.sm_count;
+  if (d_status) *d_status = s.d_status;
+  return CSW_OK;
+}
+
+static bool valid_maxbits(unsigned maxbits) {
+  // 9 header bits must fit (below that the reference overruns the block,
+  // encode.cuh:360-366); 64 planes of 64 bits plus group tests bound the top
+  return maxbits >= 9 && maxbits <= 4096;
+}
+
+}  // namespace csw
+
+using namespace csw;
+
+extern "C" {
+
+const char* csw_status_string(csw_status s) {
+  switch (s) {
+    case CSW_OK: return "ok";
+    case CSW_ERR_ARG: return "bad argument";
+    case CSW_ERR_SIZE: return "output capacity too small";
+    case CSW_ERR_CUDA: return "CUDA runtime error";
+    case CSW_ERR_NOMEM: return "out of pool memory";
+    case CSW_ERR_STATE: return "invalid state for this call";
+    case CSW_ERR_TIMEOUT: return "bounded device wait ran out";
+    case CSW_ERR_UNSUPPORTED: return "unsupported";
+    default: return "unknown status";
+  }
+}
+
+int csw_last_cuda_error(void) { return tl_cuda_error; }
+const char* csw_version(void) { return "0.1.0"; }
+
+csw_status csw_device_status(csw_stream_t stream) {
+  int* d_status = nullptr;
+  csw_status st = device_state(nullptr, &d_status);
+  if (st != CSW_OK) return st;
+  cudaError_t e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return cuda_fail(e);
+  int h = 0;
+  e = cudaMemcpy(&h, d_status, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (h != 0) {
+    e = cudaMemset(d_status, 0, sizeof(int));
+    if (e != cudaSuccess) return cuda_fail(e);
+    return CSW_ERR_TIMEOUT;
+  }
+  return CSW_OK;
+}
+
+// ---- ZFP --------------------------------------------------------------------------
+csw_status csw_zfp_max_bytes(size_t nx, size_t ny, size_t nz, unsigned maxbits, size_t* bytes) {
+  if (!bytes || !valid_maxbits(maxbits)) return CSW_ERR_ARG;
+  if (nx == 0 || (ny == 0 && nz != 0)) return CSW_ERR_ARG;
+  *bytes = stream_bytes(make_geom(nx, ny, nz, 0, 0, 0), maxbits);
+  return CSW_OK;
+}
+
+csw_status csw_zfp_view(size_t numel, size_t* nx, size_t* ny, size_t* nz) {
+  if (!nx || !ny || !nz) return CSW_ERR_ARG;
+  if (numel == 0 || numel % 1024) return CSW_ERR_UNSUPPORTED;
+  *nx = 32;
+  *ny = 32;
+  *nz = numel / 1024;
+  return CSW_OK;
+}
+
+static csw_status check_field(size_t nx, size_t ny, size_t nz, unsigned maxbits) {
+  if (!valid_maxbits(maxbits)) return CSW_ERR_ARG;
+  if (nx == 0 || (ny == 0 && nz != 0)) return CSW_ERR_ARG;
+  if (nx > 0xfffffffcu || ny > 0xfffffffcu || nz > 0xfffffffcu) return CSW_ERR_ARG;
+  return CSW_OK;
+}
+
+csw_status csw_zfp_compress_strided(const float* d_in, size_t nx, size_t ny, size_t nz, ptrdiff_t sx, ptrdiff_t sy,
+                                    ptrdiff_t sz, unsigned maxbits, void* d_out, size_t cap, size_t* bytes,
+                                    csw_stream_t stream) {
+  csw_status st = check_field(nx, ny, nz, maxbits);
+  if (st != CSW_OK) return st;
+  if (!d_in || !d_out) return CSW_ERR_ARG;
+  const FieldGeom g = make_geom(nx, ny, nz, sx, sy, sz);
+  const size_t need = stream_bytes(g, maxbits);
+  if (bytes) *bytes = need;
+  if (cap < need) return CSW_ERR_SIZE;
+  int sms = 0;
+  int* d_status = nullptr;
+  st = device_state(&sms, &d_status);
+  if (st != CSW_OK) return st;
+  cudaError_t e = zfp_encode_launch(g, d_in, d_out, (int)maxbits, sms, d_status, stream);
+  return e == cudaSuccess ? CSW_OK : cuda_fail(e);
+}
+
+csw_status csw_zfp_compress(const float* d_in, size_t nx, size_t ny, size_t nz, unsigned maxbits, void* d_out,
+                            size_t cap, size_t* bytes, csw_stream_t stream) {
+  return csw_zfp_compress_strided(d_in, nx, ny, nz, 0, 0, 0, maxbits, d_out, cap, bytes, stream);
+}
+
+csw_status csw_zfp_decompress_strided(const void* d_in, size_t bytes, size_t nx, size_t ny, size_t nz, ptrdiff_t sx,
+                                      ptrdiff_t sy, ptrdiff_t sz, unsigned maxbits, float* d_out,
+                                      csw_stream_t stream) {
+  csw_status st = check_field(nx, ny, nz, maxbits);
+  if (st != CSW_OK) return st;
+  if (!d_in || !d_out) return CSW_ERR_ARG;
+  const FieldGeom g = make_geom(nx, ny, nz, sx, sy, sz);
+  if (bytes < stream_bytes(g, maxbits)) return CSW_ERR_SIZE;
+  int sms = 0;
+  int* d_status = nullptr;
+  st = device_state(&sms, &d_status);
+  if (st != CSW_OK) return st;
+  cudaError_t e = zfp_decode_launch(g, d_in, d_out, (int)maxbits, sms, d_status, stream);
+  return e == cudaSuccess ? CSW_OK : cuda_fail(e);
+}
+
+csw_status csw_zfp_decompress(const void* d_in, size_t bytes, size_t nx, size_t ny, size_t nz, unsigned maxbits,
+                              float* d_out, csw_stream_t stream) {
+  return csw_zfp_decompress_strided(d_in, bytes, nx, ny, nz, 0, 0, 0, maxbits, d_out, stream);
+}
+
+// ---- sparse -------------------------------------------------------------------------
+static size_t align16(size_t x) { return (x + 15) & ~(size_t)15; }
+
+csw_status csw_sparse_layout_of(size_t n, csw_sparse_layout* L) {
+  if (!L) return CSW_ERR_ARG;
+  if (n > 0xffffffffull) return CSW_ERR_ARG;  // value offsets are 32-bit
+  const size_t tiles = (n + SPARSE_TILE - 1) / SPARSE_TILE, words = (n + 31) / 32;
+  L->tile_off = 0;
+  L->bitmap = align16(tiles * 4);
+  L->values = L->bitmap + align16(words * 4);
+  L->bound = L->values + align16(n * 4);
+  return CSW_OK;
+}
+
+csw_status csw_sparse_compress(const float* d_in, size_t n, void* d_out, size_t cap, uint32_t* nnz_out,
+                               csw_stream_t stream) {
+  csw_sparse_layout L;
+  csw_status st = csw_sparse_layout_of(n, &L);
+  if (st != CSW_OK) return st;
+  if ((!d_in && n) || !d_out || !nnz_out) return CSW_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(d_out) & 15) != 0) return CSW_ERR_ARG;
+  if (cap < L.bound) return CSW_ERR_SIZE;
+  char* base = static_cast<char*>(d_out);
+  cudaError_t e = sparse_compress_launch(d_in, n, reinterpret_cast<uint32_t*>(base + L.bitmap),
+                                         reinterpret_cast<float*>(base + L.values),
+                                         reinterpret_cast<uint32_t*>(base + L.tile_off), nnz_out, stream);
+  return e == cudaSuccess ? CSW_OK : cuda_fail(e);
+}
+
+csw_status csw_sparse_decompress(const void* d_in, size_t n, float* d_out, csw_stream_t stream) {
+  csw_sparse_layout L;
+  csw_status st = csw_sparse_layout_of(n, &L);
+  if (st != CSW_OK) return st;
+  if (!d_in || (!d_out && n)) return CSW_ERR_ARG;
+  const char* base = static_cast<const char*>(d_in);
+  cudaError_t e = sparse_decompress_launch(reinterpret_cast<const uint32_t*>(base + L.bitmap),
+                                           reinterpret_cast<const float*>(base + L.values),
+                                           reinterpret_cast<const uint32_t*>(base + L.tile_off), n, d_out, stream);
+  return e == cudaSuccess ? CSW_OK : cuda_fail(e);
+}
+
+// ---- pinned host memory -------------------------------------------------------------
+csw_status csw_host_alloc(size_t bytes, void** p) {
+  if (!p) return CSW_ERR_ARG;
+  cudaError_t e = cudaHostAlloc(p, bytes ? bytes : 1, cudaHostAllocDefault);
+  return e == cudaSuccess ? CSW_OK : cuda_fail(e);
+}
+csw_status csw_host_free(void* p) {
+  cudaError_t e = cudaFreeHost(p);
+  return e == cudaSuccess ? CSW_OK : cuda_fail(e);
+}
+
+// =====================================================================================
+// entry points with the reference's names
+// =====================================================================================
+static void legacy_report(const char* where, cudaError_t e) {
+  if (e != cudaSuccess) {
+    tl_cuda_error = (int)e;
+    std::fprintf(stderr, "cswap_b200: %s: %s\n", where, cudaGetErrorString(e));
+  }
+}
+
+void PreGPUcompression(int arraySize, int kernelSize, float* arrayGPU, int* valueIndex, int, int,
+                       csw_stream_t stream) {
+  legacy_report("PreGPUcompression", legacy_count_launch(arraySize, kernelSize, arrayGPU, valueIndex, stream));
+}
+void PreAcc(int* valueIndex, int KernelSize, int* num, int, int, csw_stream_t stream) {
+  legacy_report("PreAcc", legacy_scan_launch(valueIndex, KernelSize, num, stream));
+}
+void GPUcompression(int arraySize, int kernelSize, float* arrayGPU, float* compressedList, int* compressedValueIndex,
+                    uint32_t* compressedBinIndex, int, int, csw_stream_t stream) {
+  legacy_report("GPUcompression", legacy_pack_launch(arraySize, kernelSize, arrayGPU, compressedList,
+                                                     compressedValueIndex, compressedBinIndex, stream));
+}
+void GPUdecompression(float* arrayGPU, float* destiGPU, int arraySize, int kernelSize, uint32_t* gpuDataindex,
+                      int* beginIndex, int, int) {
+  legacy_report("GPUdecompression",
+                legacy_unpack_launch(arrayGPU, destiGPU, arraySize, kernelSize, gpuDataindex, beginIndex, nullptr));
+}
+
+// ---- cuda_compress / cuda_decompress ------------------------------------------------
+namespace {
+
+bool is_device_ptr(const void* p) {
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+// grow-only device staging for callers that hand in host memory (the
+// reference cudaMallocs and frees per call, cuZFP.cu:205-304)
+struct Staging {
+  void* p = nullptr;
+  size_t cap = 0;
+  int dev = -1;
+  cudaError_t reserve(size_t bytes) {
+    int d = 0;
+    cudaError_t e = cudaGetDevice(&d);
+    if (e != cudaSuccess) return e;
+    if (p && (d != dev || cap < bytes)) {
+      cudaFree(p);
+      p = nullptr;
+      cap = 0;
+    }
+    if (!p) {
+      e = cudaMalloc(&p, bytes ? bytes : 16);
+      if (e != cudaSuccess) return e;
+      cap = bytes;
+      dev = d;
+    }
+    return cudaSuccess;
+  }
+};
+std::mutex g_legacy_mu;
+Staging g_field_stage, g_stream_stage;
+
+bool contiguous(const csw_zfp_field* f) {
+  const ptrdiff_t sx = f->sx ? f->sx : 1, sy = f->sy ? f->sy : (ptrdiff_t)f->nx,
+                  sz = f->sz ? f->sz : (ptrdiff_t)(f->nx * (f->ny ? f->ny : 1));
+  return sx == 1 && (f->ny == 0 || sy == (ptrdiff_t)f->nx) && (f->nz == 0 || sz == (ptrdiff_t)(f->nx * f->ny));
+}
+size_t field_values(const csw_zfp_field* f) { return f->nx * (f->ny ? f->ny : 1) * (f->nz ? f->nz : 1); }
+
+}  // namespace
+
+size_t cuda_compress(csw_zfp_stream* zs, const csw_zfp_field* f) {
+  if (!zs || !zs->stream || !zs->stream->begin || !f || !f->data) return 0;
+  if (f->type != 3 || f->nw != 0) {
+    std::fprintf(stderr, "cswap_b200: cuda_compress: only float32 fields of up to 3 dimensions are supported\n");
+    return 0;
+  }
+  std::lock_guard<std::mutex> lk(g_legacy_mu);
+  const unsigned maxbits = zs->maxbits;
+  size_t bytes = 0;
+  if (csw_zfp_max_bytes(f->nx, f->ny, f->nz, maxbits, &bytes) != CSW_OK) return 0;
+  const bool field_dev = is_device_ptr(f->data), stream_dev = is_device_ptr(zs->stream->begin);
+  const float* d_field = static_cast<const float*>(f->data);
+  ptrdiff_t sx = f->sx, sy = f->sy, sz = f->sz;
+  if (!field_dev) {
+    if (!contiguous(f)) return 0;  // as the reference: strided host arrays are refused (cuZFP.cu:381-385)
+    const size_t fb = field_values(f) * sizeof(float);
+    cudaError_t e = g_field_stage.reserve(fb);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(g_field_stage.p, f->data, fb, cudaMemcpyHostToDevice, nullptr);
+    if (e != cudaSuccess) { legacy_report("cuda_compress", e); return 0; }
+    d_field = static_cast<const float*>(g_field_stage.p);
+    sx = sy = sz = 0;
+  }
+  void* d_stream = zs->stream->begin;
+  if (!stream_dev) {
+    cudaError_t e = g_stream_stage.reserve(bytes);
+    if (e != cudaSuccess) { legacy_report("cuda_compress", e); return 0; }
+    d_stream = g_stream_stage.p;
+  }
+  csw_status st = csw_zfp_compress_strided(d_field, f->nx, f->ny, f->nz, sx, sy, sz, maxbits, d_stream, bytes, nullptr,
+                                           nullptr);
+  if (st != CSW_OK) return 0;
+  cudaError_t e = cudaSuccess;
+  if (!stream_dev) e = cudaMemcpyAsync(zs->stream->begin, d_stream, bytes, cudaMemcpyDeviceToHost, nullptr);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(nullptr);
+  if (e != cudaSuccess) { legacy_report("cuda_compress", e); return 0; }
+  // what zfp expects after a flush (cuZFP.cu:428-433)
+  zs->stream->bits = 64;
+  zs->stream->ptr = zs->stream->begin + bytes / 8;
+  return bytes;
+}
+
+void cuda_decompress(csw_zfp_stream* zs, csw_zfp_field* f) {
+  if (!zs || !zs->stream || !zs->stream->begin || !f || !f->data) return;
+  if (f->type != 3 || f->nw != 0) {
+    std::fprintf(stderr, "cswap_b200: cuda_decompress: only float32 fields of up to 3 dimensions are supported\n");
+    return;
+  }
+  std::lock_guard<std::mutex> lk(g_legacy_mu);
+  const unsigned maxbits = zs->maxbits;
+  size_t bytes = 0;
+  if (csw_zfp_max_bytes(f->nx, f->ny, f->nz, maxbits, &bytes) != CSW_OK) return;
+  const bool field_dev = is_device_ptr(f->data), stream_dev = is_device_ptr(zs->stream->begin);
+  float* d_field = static_cast<float*>(f->data);
+  ptrdiff_t sx = f->sx, sy = f->sy, sz = f->sz;
+  const size_t fb = field_values(f) * sizeof(float);
+  if (!field_dev) {
+    if (!contiguous(f)) return;
+    cudaError_t e = g_field_stage.reserve(fb);
+    if (e != cudaSuccess) { legacy_report("cuda_decompress", e); return; }
+    d_field = static_cast<float*>(g_field_stage.p);
+    sx = sy = sz = 0;
+  }
+  const void* d_stream = zs->stream->begin;
+  if (!stream_dev) {
+    cudaError_t e = g_stream_stage.reserve(bytes);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(g_stream_stage.p, zs->stream->begin, bytes, cudaMemcpyHostToDevice, nullptr);
+    if (e != cudaSuccess) { legacy_report("cuda_decompress", e); return; }
+    d_stream = g_stream_stage.p;
+  }
+  csw_status st =
+      csw_zfp_decompress_strided(d_stream, bytes, f->nx, f->ny, f->nz, sx, sy, sz, maxbits, d_field, nullptr);
+  if (st != CSW_OK) return;
+  cudaError_t e = cudaSuccess;
+  if (!field_dev) e = cudaMemcpyAsync(f->data, d_field, fb, cudaMemcpyDeviceToHost, nullptr);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(nullptr);
+  if (e != cudaSuccess) { legacy_report("cuda_decompress", e); return; }
+  zs->stream->bits = 64;
+  zs->stream->ptr = zs->stream->begin + bytes / 8;
+}
+
+}  // extern "C"

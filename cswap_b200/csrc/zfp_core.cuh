@@ -1,0 +1,562 @@
+// Block-level arithmetic of the fixed-rate ZFP float32 codec, written for one
+// thread holding one whole block in registers (lane = block).
+//
+// Format follows cuZFP as vendored by CSWAP+ (CSWAP+/zfp/encode.cuh:306-368,
+// decode.cuh:127-288, shared.h:176-250, constants.h:8-131): 1 flag bit + 8-bit
+// biased block exponent, block-floating-point cast to int32, passes of the
+// 4-point lifting transform, sequency reorder + negabinary, then the embedded
+// group-tested bit-plane coder cut at `maxbits` bits per block.
+//
+// What differs from the reference is only how the same bits are produced:
+//  * bit planes come from 8x8 bit-matrix transposes of the coefficient bytes
+//    (PRMT gathers + 3 masked swap stages), eight planes at a time, instead of
+//    a 64-step gather per plane;
+//  * the group-test phase of a plane is expanded (encoder) or parsed (decoder)
+//    eight positions / stream bits per step through small tables held in
+//    shared memory instead of one stream bit per step;
+//  * coded bits are assembled in a 64-bit register window and leave as whole
+//    32-bit words - no atomics and no pre-zeroed output.
+//
+// Everything here is plain scalar code per block, so the same header also
+// compiles for the host (tests drive it lane by lane against the CPU oracle).
+#pragma once
+#include <cstdint>
+#include <utility>
+
+#if defined(__CUDACC__)
+#define CSW_HD __host__ __device__ __forceinline__
+#else
+#define CSW_HD inline
+#endif
+
+namespace csw {
+
+// ---- portable intrinsics ------------------------------------------------------
+CSW_HD uint32_t byte_perm(uint32_t a, uint32_t b, uint32_t s) {
+#if defined(__CUDA_ARCH__)
+  return __byte_perm(a, b, s);
+#else
+  uint64_t ab = ((uint64_t)b << 32) | a;
+  uint32_t r = 0;
+  for (int i = 0; i < 4; i++) r |= (uint32_t)((ab >> (8 * ((s >> (4 * i)) & 7))) & 0xff) << (8 * i);
+  return r;
+#endif
+}
+CSW_HD int clz64(uint64_t x) {
+#if defined(__CUDA_ARCH__)
+  return __clzll((long long)x);
+#else
+  return x ? __builtin_clzll(x) : 64;
+#endif
+}
+CSW_HD int clz32(uint32_t x) {
+#if defined(__CUDA_ARCH__)
+  return __clz((int)x);
+#else
+  return x ? __builtin_clz(x) : 32;
+#endif
+}
+CSW_HD int popc32(uint32_t x) {
+#if defined(__CUDA_ARCH__)
+  return __popc(x);
+#else
+  return __builtin_popcount(x);
+#endif
+}
+CSW_HD uint32_t f2u(float f) {
+#if defined(__CUDA_ARCH__)
+  return __float_as_uint(f);
+#else
+  union { float f; uint32_t u; } c; c.f = f; return c.u;
+#endif
+}
+CSW_HD float u2f(uint32_t u) {
+#if defined(__CUDA_ARCH__)
+  return __uint_as_float(u);
+#else
+  union { float f; uint32_t u; } c; c.u = u; return c.f;
+#endif
+}
+// float -> int32, round toward zero, saturating, NaN -> 0 (cvt.rzi.s32.f32)
+CSW_HD int f2i_rz(float f) {
+#if defined(__CUDA_ARCH__)
+  return __float2int_rz(f);
+#else
+  if (f != f) return 0;
+  if (f >= 2147483648.0f) return 2147483647;
+  if (f <= -2147483648.0f) return (int)0x80000000;
+  return (int)f;
+#endif
+}
+CSW_HD uint32_t low_mask32(int n) {  // n in 0..32
+  return n >= 32 ? 0xffffffffu : ((1u << n) - 1u);
+}
+
+// ---- sequency order (constants.h:8-131), entries are x + 4y + 16z ---------------
+constexpr int perm3(int i) {
+  constexpr unsigned char t[64] = {
+      0,  1,  4,  16, 20, 17, 5,  2,  8,  32, 21, 6,  18, 24, 9,  33,
+      36, 3,  12, 48, 22, 25, 37, 40, 34, 10, 7,  19, 28, 13, 49, 52,
+      41, 38, 26, 23, 29, 53, 11, 35, 44, 14, 50, 56, 42, 27, 39, 45,
+      30, 54, 57, 60, 51, 15, 43, 46, 58, 61, 55, 31, 62, 59, 47, 63};
+  return t[i];
+}
+constexpr int perm2(int i) {
+  constexpr unsigned char t[16] = {0, 1, 4, 5, 2, 8, 6, 9, 3, 12, 10, 7, 13, 11, 14, 15};
+  return t[i];
+}
+template <int DIMS, int I>
+struct PermAt {
+  static constexpr int v = DIMS == 3 ? perm3(I & 63) : DIMS == 2 ? perm2(I & 15) : I;
+};
+
+// ---- lifting (encode.cuh:73-99, shared.h:221-250) --------------------------------
+// Arithmetic is done on unsigned patterns where C++ would overflow; the GPU
+// reference simply wraps.
+CSW_HD int wadd(int a, int b) { return (int)((uint32_t)a + (uint32_t)b); }
+CSW_HD int wsub(int a, int b) { return (int)((uint32_t)a - (uint32_t)b); }
+CSW_HD void fwd_lift(int& x, int& y, int& z, int& w) {
+  x = wadd(x, w); x >>= 1; w = wsub(w, x);
+  z = wadd(z, y); z >>= 1; y = wsub(y, z);
+  x = wadd(x, z); x >>= 1; z = wsub(z, x);
+  w = wadd(w, y); w >>= 1; y = wsub(y, w);
+  w = wadd(w, y >> 1); y = wsub(y, w >> 1);
+}
+CSW_HD int twice_minus(int a, int b) { return (int)(((uint32_t)a << 1) - (uint32_t)b); }
+CSW_HD void inv_lift(int& x, int& y, int& z, int& w) {
+  y = wadd(y, w >> 1); w = wsub(w, y >> 1);
+  y = wadd(y, w); w = twice_minus(w, y);
+  z = wadd(z, x); x = twice_minus(x, z);
+  y = wadd(y, z); z = twice_minus(z, y);
+  w = wadd(w, x); x = twice_minus(x, w);
+}
+
+template <int DIMS>
+CSW_HD void fwd_xform(int (&v)[1 << (2 * DIMS)]) {
+  if constexpr (DIMS == 3) {
+#pragma unroll
+    for (int i = 0; i < 16; i++) fwd_lift(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+#pragma unroll
+    for (int z = 0; z < 4; z++)
+#pragma unroll
+      for (int x = 0; x < 4; x++)
+        fwd_lift(v[16 * z + x], v[16 * z + x + 4], v[16 * z + x + 8], v[16 * z + x + 12]);
+#pragma unroll
+    for (int i = 0; i < 16; i++) fwd_lift(v[i], v[i + 16], v[i + 32], v[i + 48]);
+  } else if constexpr (DIMS == 2) {
+#pragma unroll
+    for (int y = 0; y < 4; y++) fwd_lift(v[4 * y], v[4 * y + 1], v[4 * y + 2], v[4 * y + 3]);
+#pragma unroll
+    for (int x = 0; x < 4; x++) fwd_lift(v[x], v[x + 4], v[x + 8], v[x + 12]);
+  } else {
+    fwd_lift(v[0], v[1], v[2], v[3]);
+  }
+}
+
+template <int DIMS>
+CSW_HD void inv_xform(int (&v)[1 << (2 * DIMS)]) {
+  if constexpr (DIMS == 3) {
+#pragma unroll
+    for (int i = 0; i < 16; i++) inv_lift(v[i], v[i + 16], v[i + 32], v[i + 48]);
+#pragma unroll
+    for (int z = 0; z < 4; z++)
+#pragma unroll
+      for (int x = 0; x < 4; x++)
+        inv_lift(v[16 * z + x], v[16 * z + x + 4], v[16 * z + x + 8], v[16 * z + x + 12]);
+#pragma unroll
+    for (int i = 0; i < 16; i++) inv_lift(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  } else if constexpr (DIMS == 2) {
+#pragma unroll
+    for (int x = 0; x < 4; x++) inv_lift(v[x], v[x + 4], v[x + 8], v[x + 12]);
+#pragma unroll
+    for (int y = 0; y < 4; y++) inv_lift(v[4 * y], v[4 * y + 1], v[4 * y + 2], v[4 * y + 3]);
+  } else {
+    inv_lift(v[0], v[1], v[2], v[3]);
+  }
+}
+
+// ---- negabinary (shared.h:176-181, decode.cuh:33-37) ------------------------------
+CSW_HD uint32_t int2uint(int x) { return ((uint32_t)x + 0xaaaaaaaau) ^ 0xaaaaaaaau; }
+CSW_HD int uint2int(uint32_t x) { return (int)((x ^ 0xaaaaaaaau) - 0xaaaaaaaau); }
+
+template <int DIMS, int... I>
+CSW_HD void fwd_order(const int (&v)[sizeof...(I)], uint32_t (&u)[sizeof...(I)], std::integer_sequence<int, I...>) {
+  ((u[I] = int2uint(v[PermAt<DIMS, I>::v])), ...);
+}
+template <int DIMS, int... I>
+CSW_HD void inv_order(const uint32_t (&u)[sizeof...(I)], int (&v)[sizeof...(I)], std::integer_sequence<int, I...>) {
+  ((v[PermAt<DIMS, I>::v] = uint2int(u[I])), ...);
+}
+
+// ---- block exponent and cast (encode.cuh:40-71,120-149) ---------------------------
+// Biased exponent field e = emax + 127 (0 for an all-zero block) from the bit
+// pattern of max|v|: frexp's exponent of a normal float with exponent field E
+// is E - 126, and denormals are floored at -126 (field 1).
+CSW_HD uint32_t biased_emax(float maxabs) {
+  uint32_t b = f2u(maxabs);
+  return b == 0 ? 0u : (b >> 23) + 1u;
+}
+// 2^(30 - emax) as a float; +inf for emax < -97, exactly what the reference's
+// ldexp-then-narrow yields, so with the saturating conversion such
+// (denormal-range) blocks code the way the reference codes them on a GPU.
+CSW_HD float quant_scale(uint32_t e) {
+  int f = 284 - (int)e;  // exponent field of 2^(30-emax), emax = e - 127
+  f = f > 255 ? 255 : f;
+  return u2f((uint32_t)f << 23);
+}
+// 2^(emax - 30) (shared.h:197-203, decode.cuh:278); denormal below emax = -96.
+CSW_HD float dequant_scale(uint32_t e) {
+  int f = (int)e - 30;  // exponent field of 2^(emax-30) = e - 127 - 30 + 127
+  if (f >= 1) return u2f((uint32_t)f << 23);
+  return f > -23 ? u2f(1u << (22 + f)) : 0.0f;  // denormal results of ldexp
+}
+
+// ---- 8-plane slices by bit-matrix transpose ---------------------------------------
+// One masked swap of an 8x8 (per byte lane) bit transpose.
+template <int S, uint32_t M>
+CSW_HD void tswap(uint32_t& a, uint32_t& b) {
+  uint32_t na = (a & M) | ((b << S) & ~M);
+  uint32_t nb = ((a >> S) & M) | (b & ~M);
+  a = na;
+  b = nb;
+}
+// In every byte lane: bit k of word j <-> bit j of word k.  Its own inverse.
+CSW_HD void transpose8(uint32_t (&r)[8]) {
+#pragma unroll
+  for (int j = 0; j < 4; j++) tswap<4, 0x0f0f0f0fu>(r[j], r[j + 4]);
+#pragma unroll
+  for (int j = 0; j < 8; j += 4) {
+    tswap<2, 0x33333333u>(r[j], r[j + 2]);
+    tswap<2, 0x33333333u>(r[j + 1], r[j + 3]);
+  }
+#pragma unroll
+  for (int j = 0; j < 8; j += 2) tswap<1, 0x55555555u>(r[j], r[j + 1]);
+}
+
+// p[k] (k = 0..7) <- bit (8c + k) of coefficients 32G .. 32G+31, coefficient
+// 32G + i at bit i.  Byte m of gather word j holds coefficient 8m + j, so after
+// the transpose bit 8m + j of a plane word is coefficient 8m + j.
+// sel = c | (4 + c) << 4 picks byte c of both PRMT operands.
+template <int G, int N>
+CSW_HD void planes_of_byte(const uint32_t (&u)[N], uint32_t sel, uint32_t (&p)[8]) {
+  static_assert(N == 64 || N == 16 || N == 4, "block size");
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    if constexpr (N == 64) {
+      uint32_t t0 = byte_perm(u[32 * G + j], u[32 * G + 8 + j], sel);
+      uint32_t t1 = byte_perm(u[32 * G + 16 + j], u[32 * G + 24 + j], sel);
+      p[j] = byte_perm(t0, t1, 0x5410);
+    } else if constexpr (N == 16) {
+      p[j] = byte_perm(u[j], u[8 + j], sel) & 0xffffu;
+    } else {
+      p[j] = j < 4 ? (byte_perm(u[j & 3], 0, sel) & 0xffu) : 0u;
+    }
+  }
+  transpose8(p);
+}
+
+// Inverse: write byte c of each coefficient from eight plane words.
+// sel0 keeps the other three bytes of the destination and takes byte 0 of the
+// second PRMT operand into byte c; adding m << 4c takes byte m instead.
+template <int G, int N>
+CSW_HD void bytes_from_planes(uint32_t (&p)[8], uint32_t sel0, uint32_t step, uint32_t (&u)[N]) {
+  transpose8(p);
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    if constexpr (N == 64) {
+#pragma unroll
+      for (int m = 0; m < 4; m++) u[32 * G + 8 * m + j] = byte_perm(u[32 * G + 8 * m + j], p[j], sel0 + m * step);
+    } else if constexpr (N == 16) {
+      u[j] = byte_perm(u[j], p[j], sel0);
+      u[8 + j] = byte_perm(u[8 + j], p[j], sel0 + step);
+    } else {
+      if (j < 4) u[j & 3] = byte_perm(u[j & 3], p[j], sel0);
+    }
+  }
+}
+
+// ---- coder tables -----------------------------------------------------------------
+// Encoder: entry for the eight positions v of a plane word past the already
+// significant prefix.  Each 0 position codes as '0'; each 1 position codes as
+// '1' followed by the next group-test bit, which is '1' whenever a later set
+// bit exists.  bits 0..15: that pattern; bits 16..20: its length 8 + popc(v);
+// bits 24..28: length when the byte holds the last set bit of the plane
+// (positions up to the top set bit, plus one per set bit; the final group-test
+// bit is then the '0' terminator).
+constexpr int ENC_LUT_SIZE = 256;
+CSW_HD uint32_t enc_lut_entry(uint32_t v) {
+  uint32_t pat = 0;
+  int len = 0, top = -1, ones = 0;
+  for (int i = 0; i < 8; i++) {
+    if ((v >> i) & 1u) {
+      pat |= 3u << len;
+      len += 2;
+      top = i;
+      ones++;
+    } else {
+      len += 1;
+    }
+  }
+  uint32_t lf = top < 0 ? 0u : (uint32_t)(top + 1 + ones);
+  return pat | ((uint32_t)len << 16) | (lf << 24);
+}
+
+// Decoder: entry for (limit L in 1..8, state, next stream byte).  Simulates the
+// group-test parser of decode.cuh:147-164 over at most L stream bits.
+// State 0: expecting a group-test bit; state 1: inside a unary run (expecting
+// value bits until a one); state 2: negative group test seen, plane finished.
+// bits 0..3: stream bits consumed; bits 4..7: positions advanced;
+// bits 8..15: plane bits found, relative to the starting position;
+// bits 16..17: state afterwards.
+constexpr int DEC_LUT_SIZE = 8 * 2 * 256;
+CSW_HD int dec_lut_index(int L, int state, uint32_t byte) { return ((L - 1) * 2 + state) * 256 + (int)byte; }
+CSW_HD uint32_t dec_lut_entry(int idx) {
+  uint32_t byte = idx & 255;
+  int st = (idx >> 8) & 1, L = (idx >> 9) + 1;
+  int c = 0, dn = 0;
+  uint32_t pat = 0;
+  while (c < L) {
+    uint32_t bit = (byte >> c) & 1u;
+    c++;
+    if (st == 0) {
+      if (bit) st = 1;
+      else { st = 2; break; }
+    } else {
+      if (bit) { pat |= 1u << dn; st = 0; }
+      dn++;
+    }
+  }
+  return (uint32_t)c | ((uint32_t)dn << 4) | (pat << 8) | ((uint32_t)st << 16);
+}
+
+// ---- bit emitter ------------------------------------------------------------------
+// WordSink::put(w, word) receives the block's w-th 32-bit stream word; words
+// arrive in increasing w, each once.
+template <class WordSink>
+struct Emitter {
+  uint64_t acc;
+  int fill;   // valid bits in acc, < 32 between calls
+  int wpos;   // words already handed to the sink
+  int nwords; // ceil(maxbits / 32)
+  WordSink& sink;
+  CSW_HD Emitter(WordSink& s, int nw) : acc(0), fill(0), wpos(0), nwords(nw), sink(s) {}
+  CSW_HD int total() const { return 32 * wpos + fill; }
+  // append the low `len` (0..32) bits of v; bits of v above len must be zero
+  CSW_HD void emit(uint32_t v, int len) {
+    acc |= (uint64_t)v << fill;
+    fill += len;
+    if (fill >= 32) {
+      if (wpos < nwords) sink.put(wpos, (uint32_t)acc);
+      wpos++;
+      acc >>= 32;
+      fill -= 32;
+    }
+  }
+  // hand over whatever is buffered and zero-fill the rest of the block
+  CSW_HD void finish() {
+    while (wpos < nwords) {
+      sink.put(wpos, (uint32_t)acc);
+      acc >>= 32;
+      wpos++;
+    }
+  }
+};
+
+// ---- encoder: one plane -----------------------------------------------------------
+// Codes plane word x (coefficient i at bit i, N coefficients) given n already
+// significant coefficients (encode.cuh:336-343).  Emission ignores the bit
+// budget: the stream is an exact prefix of the unlimited-budget stream, so the
+// caller stops once total() reaches maxbits and the emitter drops the overrun.
+template <int N, class WordSink>
+CSW_HD void encode_plane(uint64_t x, int& n, Emitter<WordSink>& em, const uint32_t* enc_lut) {
+  // step 2: first n bits verbatim
+  if (n > 0) {
+    if (n <= 32) {
+      em.emit((uint32_t)x & low_mask32(n), n);
+    } else {
+      em.emit((uint32_t)x, 32);
+      em.emit((uint32_t)(x >> 32) & low_mask32(n - 32), n - 32);
+    }
+  }
+  if (n >= N) return;
+  // step 3: group tests + unary runs over the remaining positions
+  uint64_t xs = x >> n;
+  if (xs == 0) {
+    em.emit(0u, 1);
+    return;
+  }
+  em.emit(1u, 1);
+  const int top = (int)((x >> (N - 1)) & 1u);  // last position set: its 1 is implied
+  for (;;) {
+    uint32_t e = enc_lut[(uint32_t)xs & 0xffu];
+    xs >>= 8;
+    if (xs != 0) {
+      em.emit(e & 0xffffu, (int)((e >> 16) & 0x1fu));
+    } else {
+      int lf = (int)(e >> 24);
+      // drop the '0' terminator slot from the pattern; when the plane ends on
+      // the last position neither its 1 nor a terminator is coded
+      em.emit(e & 0xffffu & low_mask32(lf - 1 - top), lf - 2 * top);
+      break;
+    }
+  }
+  int msb = 64 - clz64(x);
+  n = n > msb ? n : msb;
+}
+
+// ---- encoder: whole block ---------------------------------------------------------
+// f: the block's values, x fastest (index x + 4y + 16z).  Produces exactly
+// ceil(maxbits/32) words through the sink (the last one masked by the caller
+// when maxbits is not a multiple of 32).
+template <int DIMS, class WordSink>
+CSW_HD void encode_block(const float (&f)[1 << (2 * DIMS)], int maxbits, WordSink& sink, const uint32_t* enc_lut) {
+  constexpr int N = 1 << (2 * DIMS);
+  Emitter<WordSink> em(sink, (maxbits + 31) >> 5);
+  float m = 0.0f;
+#pragma unroll
+  for (int i = 0; i < N; i++) m = fmaxf(m, fabsf(f[i]));
+  const uint32_t e = biased_emax(m);
+  if (e == 0) {  // all-zero block: nothing is coded (encode.cuh:356-357)
+    em.finish();
+    return;
+  }
+  em.emit((2u * e + 1u) & 0x1ffu, 9);
+  int v[N];
+  {
+    const float s = quant_scale(e);
+#pragma unroll
+    for (int i = 0; i < N; i++) v[i] = f2i_rz(s * f[i]);
+  }
+  fwd_xform<DIMS>(v);
+  uint32_t u[N];
+  fwd_order<DIMS>(v, u, std::make_integer_sequence<int, N>{});
+
+  int n = 0;
+  for (int c = 3; c >= 0; c--) {  // planes 8c+7 .. 8c
+    const uint32_t sel = (uint32_t)c | ((uint32_t)(4 + c) << 4);
+    uint32_t lo[8], hi[8];
+    planes_of_byte<0>(u, sel, lo);
+    if constexpr (N == 64) planes_of_byte<1>(u, sel, hi);
+#pragma unroll
+    for (int k = 7; k >= 0; k--) {
+      if (em.total() < maxbits) {
+        uint64_t x = lo[k];
+        if constexpr (N == 64) x |= (uint64_t)hi[k] << 32;
+        encode_plane<N>(x, n, em, enc_lut);
+      }
+    }
+    if (em.total() >= maxbits) break;
+  }
+  em.finish();
+}
+
+// ---- bit reader -------------------------------------------------------------------
+// WordSource::get(w) returns the block's w-th 32-bit stream word (0 past the
+// end of the block).
+template <class WordSource>
+struct Reader {
+  uint64_t win;
+  int avail;  // valid bits in win, >= 32 between calls
+  int wi;     // next word to fetch
+  WordSource& src;
+  CSW_HD Reader(WordSource& s) : win(0), avail(0), wi(0), src(s) {
+    win = src.get(0);
+    win |= (uint64_t)src.get(1) << 32;
+    avail = 64;
+    wi = 2;
+  }
+  CSW_HD uint32_t peek() const { return (uint32_t)win; }
+  CSW_HD void skip(int nb) {  // nb in 0..32
+    win >>= nb;
+    avail -= nb;
+    if (avail < 32) {
+      win |= (uint64_t)src.get(wi) << avail;
+      wi++;
+      avail += 32;
+    }
+  }
+  CSW_HD uint32_t take(int nb) {  // nb in 0..32
+    uint32_t r = peek() & low_mask32(nb);
+    skip(nb);
+    return r;
+  }
+};
+
+// ---- decoder: one plane -----------------------------------------------------------
+// decode.cuh:141-165 for one plane; returns the plane word.
+template <int N, class WordSource>
+CSW_HD uint64_t decode_plane(Reader<WordSource>& rd, int& n, int& bits, const uint32_t* dec_lut) {
+  // step 1: first min(n, bits) bits verbatim
+  int m = n < bits ? n : bits;
+  bits -= m;
+  uint64_t x;
+  if (m <= 32) {
+    x = rd.take(m);
+  } else {
+    x = rd.take(32);
+    x |= (uint64_t)rd.take(m - 32) << 32;
+  }
+  // step 2: group tests + unary runs
+  int st = 0;
+  for (;;) {
+    if (st == 1 && (n == N - 1 || bits == 0)) {  // run cut short: the one is implied
+      x |= (uint64_t)1 << n;
+      n++;
+      st = 0;
+    }
+    if (st == 0 && (n >= N || bits == 0)) break;
+    int lim = (st == 0 ? N : N - 1) - n;
+    int L = lim < 8 ? lim : 8;
+    L = bits < L ? bits : L;
+    uint32_t e = dec_lut[dec_lut_index(L, st, rd.peek() & 0xffu)];
+    int used = (int)(e & 0xfu);
+    x |= (uint64_t)((e >> 8) & 0xffu) << n;
+    n += (int)((e >> 4) & 0xfu);
+    bits -= used;
+    rd.skip(used);
+    st = (int)(e >> 16);
+    if (st == 2) break;
+  }
+  return x;
+}
+
+// ---- decoder: whole block ---------------------------------------------------------
+template <int DIMS, class WordSource>
+CSW_HD void decode_block(WordSource& src, int maxbits, float (&f)[1 << (2 * DIMS)], const uint32_t* dec_lut) {
+  constexpr int N = 1 << (2 * DIMS);
+  Reader<WordSource> rd(src);
+  if (!(rd.peek() & 1u)) {  // zero block (decode.cuh:240-243, decode3.cuh:72-73)
+#pragma unroll
+    for (int i = 0; i < N; i++) f[i] = 0.0f;
+    return;
+  }
+  const uint32_t e = (rd.peek() >> 1) & 0xffu;
+  rd.skip(9);
+  int bits = maxbits - 9, n = 0;
+  uint32_t u[N];
+#pragma unroll
+  for (int i = 0; i < N; i++) u[i] = 0;
+  for (int c = 3; c >= 0; c--) {
+    uint32_t lo[8], hi[8];
+#pragma unroll
+    for (int k = 7; k >= 0; k--) {
+      uint64_t x = 0;
+      if (bits > 0) x = decode_plane<N>(rd, n, bits, dec_lut);
+      lo[k] = (uint32_t)x;
+      hi[k] = (uint32_t)(x >> 32);
+    }
+    const uint32_t sel0 = (0x3210u & ~(0xfu << (4 * c))) | (4u << (4 * c));
+    const uint32_t step = 1u << (4 * c);
+    bytes_from_planes<0>(lo, sel0, step, u);
+    if constexpr (N == 64) bytes_from_planes<1>(hi, sel0, step, u);
+    if (bits <= 0) break;
+  }
+  int v[N];
+  inv_order<DIMS>(u, v, std::make_integer_sequence<int, N>{});
+  inv_xform<DIMS>(v);
+  const float w = dequant_scale(e);
+#pragma unroll
+  for (int i = 0; i < N; i++) f[i] = w * (float)v[i];
+}
+
+}  // namespace csw

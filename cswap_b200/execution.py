@@ -1,0 +1,268 @@
+"""Host-side mirror of the reference's swap orchestrator.
+
+`Execution` keeps the interface the CSWAP+ model drivers use
+(CSWAP+/Execution.h:38-447): `init_`, `preforward`, `pre`, `post`,
+`postforward`, the public tables `policy`, `begin_stage`, `index`, `policy_`,
+and the policy codes 0 keep / 2 raw / 3 sparse / 6 ZFP.  A driver wraps every
+layer as
+
+    exe.pre(x)            # may start swapping x out (Execution.h:65-133)
+    y = layer(x)
+    exe.post(x, y)        # y.tensor_id = index; x's device copy is let go
+                          # (Execution.h:217-310)
+
+and brackets the forward pass with `preforward()` / `postforward()`.
+
+The reference swaps the storage's DataPtr under the autograd graph and relies
+on a modified engine to bring it back.  On stock PyTorch the same effect is
+reached with saved-tensor hooks that stay installed for the whole forward
+pass: every activation autograd saves is held through a small record keyed by
+its storage; when `pre` swaps a tensor out, the record lets go of the device
+copy (the memory returns to the allocator once the driver's own reference is
+gone) and the first use in backward swaps it back in, prefetching the
+previously swapped tensor's payload one step ahead.
+"""
+from __future__ import annotations
+
+import enum
+import weakref
+from typing import Dict, List, Optional, Sequence, Union
+
+import torch
+
+from .codec import POLICY_DROP, POLICY_KEEP, POLICY_RAW, POLICY_SPARSE, POLICY_ZFP
+from .swap import CostModel, SwapManager, TensorDesc, Ticket
+
+
+class LayerType(enum.IntEnum):
+    """CSWAP+/Execution.h:28-35."""
+    CONV = 0
+    POOL = 1
+    ACT = 2
+    BN = 3
+    FC = 4
+    MASKFILL = 5
+
+
+class _Record:
+    """Residency of one activation storage: on the device (`tensor`) or
+    swapped out (`ticket`)."""
+
+    __slots__ = ("tensor", "ticket", "numel", "order", "exe", "__weakref__")
+
+    def __init__(self, tensor: torch.Tensor, exe: "Execution"):
+        self.tensor: Optional[torch.Tensor] = tensor
+        self.ticket: Optional[Ticket] = None
+        self.numel = tensor.numel()
+        self.order = -1
+        self.exe = weakref.ref(exe)
+
+    def materialize(self) -> torch.Tensor:
+        if self.tensor is None:
+            exe = self.exe()
+            self.tensor = exe.mgr.swap_in(self.ticket).view(-1)
+            exe._after_swap_in(self)
+        return self.tensor
+
+    def __del__(self):
+        t = self.ticket
+        if t is not None:
+            try:
+                t.release()
+            except Exception:
+                pass
+
+
+class _Packed:
+    __slots__ = ("rec", "shape", "stride", "offset")
+
+    def __init__(self, rec, shape, stride, offset):
+        self.rec, self.shape, self.stride, self.offset = rec, shape, stride, offset
+
+
+TensorOrList = Union[torch.Tensor, Sequence[torch.Tensor]]
+
+
+class Execution:
+    def __init__(self, mgr: Optional[SwapManager] = None, min_numel: int = 1024):
+        self.mgr = mgr
+        self.index = -1
+        self.policy: List[int] = []
+        self.begin_stage: List[int] = []
+        self.types: List[LayerType] = []
+        self.policy_ = 1  # 1 CSWAP, 2 Capuchin, 3 vDNN, 4 SuperNeurons (Execution.h:420)
+        self.min_numel = min_numel
+        self.profile = False
+        self._records: "weakref.WeakValueDictionary[int, _Record]" = weakref.WeakValueDictionary()
+        self._pending: List[_Record] = []
+        self._swapped: List["weakref.ref[_Record]"] = []
+        self._hooks = None
+        self._prof: Dict[int, dict] = {}
+        self._prof_start = None
+        self.swapped_tensors = 0
+
+    # ---- set-up (Execution.h:46-64) -------------------------------------------
+    def init_(self, n: int, zfp_maxbits: Optional[int] = None) -> None:
+        self.policy = [POLICY_KEEP] * n
+        self.begin_stage = [0] * n
+        if self.mgr is None:
+            self.mgr = SwapManager()
+        if zfp_maxbits is not None:
+            self.mgr.set_zfp_maxbits(zfp_maxbits)
+
+    def set_ratio(self, maxbits: int) -> None:
+        """The reference's setRatio(bits per zfp block), Execution.h:63."""
+        self.mgr.set_zfp_maxbits(maxbits)
+
+    # ---- per step (Execution.h:403-412) ----------------------------------------
+    def preforward(self) -> None:
+        self.index = -1
+        self._pending.clear()
+        self._swapped.clear()
+        if self._hooks is None:
+            self._hooks = torch.autograd.graph.saved_tensors_hooks(self._pack, self._unpack)
+            self._hooks.__enter__()
+
+    def postforward(self) -> None:
+        if self._hooks is not None:
+            self._hooks.__exit__(None, None, None)
+            self._hooks = None
+        self._pending.clear()
+
+    # ---- saved-tensor hooks ------------------------------------------------------
+    def _eligible(self, t: torch.Tensor) -> bool:
+        return (t.is_cuda and t.dtype == torch.float32 and t.numel() >= self.min_numel and t.is_contiguous()
+                and not (t.is_leaf and t.requires_grad)
+                and t.untyped_storage().nbytes() == t.numel() * 4 and t.storage_offset() == 0)
+
+    def _record_for(self, t: torch.Tensor) -> _Record:
+        key = t.untyped_storage().data_ptr()
+        rec = self._records.get(key)
+        if rec is None or rec.tensor is None or rec.tensor.untyped_storage().data_ptr() != key \
+                or rec.numel != t.numel():
+            rec = _Record(t.detach().view(-1), self)
+            self._records[key] = rec
+        return rec
+
+    def _pack(self, t: torch.Tensor):
+        if not self._eligible(t):
+            return t
+        return _Packed(self._record_for(t), t.shape, t.stride(), t.storage_offset())
+
+    def _unpack(self, p):
+        if not isinstance(p, _Packed):
+            return p
+        return p.rec.materialize().as_strided(p.shape, p.stride, p.offset)
+
+    def _after_swap_in(self, rec: _Record) -> None:
+        # one step ahead: start bringing back the tensor swapped out just before
+        for i in range(rec.order - 1, -1, -1):
+            r = self._swapped[i]() if i < len(self._swapped) else None
+            if r is not None and r.tensor is None and r.ticket is not None:
+                self.mgr.prefetch(r.ticket)
+                break
+
+    # ---- pre / post ----------------------------------------------------------------
+    def _effective_policy(self, tid: int, layer_type: LayerType) -> int:
+        pol = self.policy[tid] if tid < len(self.policy) else POLICY_KEEP
+        if layer_type == LayerType.CONV and self.policy_ > 2:
+            return POLICY_RAW  # vDNN / SuperNeurons baselines (Execution.h:70)
+        return pol
+
+    def pre(self, x: TensorOrList, layer_type: LayerType = LayerType.ACT) -> None:
+        self.index += 1
+        inputs = [x] if isinstance(x, torch.Tensor) else list(x)
+        for t in inputs:
+            tid = getattr(t, "tensor_id", -1)
+            if tid < 0 or tid >= len(self.begin_stage) or self.index != self.begin_stage[tid] or t.grad_fn is None:
+                continue
+            pol = self._effective_policy(tid, layer_type)
+            if pol not in (POLICY_RAW, POLICY_SPARSE, POLICY_ZFP) or not self._eligible(t):
+                continue
+            rec = self._record_for(t)
+            if rec.ticket is not None:
+                continue
+            rec.ticket = self.mgr.swap_out(rec.tensor, pol)
+            rec.order = len(self._swapped)
+            self._swapped.append(weakref.ref(rec))
+            self._pending.append(rec)
+            self.swapped_tensors += 1
+        if self.profile:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self._prof_start = ev
+
+    def post(self, x: TensorOrList, y: torch.Tensor, layer_type: LayerType = LayerType.ACT,
+             isomit: bool = False) -> None:
+        y.tensor_id = self.index
+        inputs = [x] if isinstance(x, torch.Tensor) else list(x)
+        if self.profile:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            zf = (y.detach() == 0).float().mean() if (y.is_cuda and y.dtype == torch.float32) else None
+            self._prof[self.index] = {
+                "start": self._prof_start, "end": ev, "numel": y.numel(), "zero_fraction": zf,
+                "inputs": [getattr(t, "tensor_id", -1) for t in inputs], "omit": isomit,
+                "type": int(layer_type), "float32": y.dtype == torch.float32, "has_grad": y.grad_fn is not None,
+            }
+        # the layer has run and saved what it needs: let go of the device copies
+        for rec in self._pending:
+            rec.tensor = None
+        self._pending.clear()
+
+    # ---- self-tuning policy (call sites Execution.h:224-233, resnet-cifar10.cpp:407-437) ---
+    def finish_profile(self) -> Dict[int, dict]:
+        """Turn the events of a profiled iteration into numbers (synchronises)."""
+        torch.cuda.synchronize()
+        out = {}
+        for idx, p in self._prof.items():
+            out[idx] = {
+                "time_s": p["start"].elapsed_time(p["end"]) * 1e-3, "numel": p["numel"],
+                "zero_fraction": float(p["zero_fraction"]) if p["zero_fraction"] is not None else -1.0,
+                "inputs": p["inputs"], "omit": p["omit"], "type": p["type"], "float32": p["float32"],
+                "has_grad": p["has_grad"],
+            }
+        self._prof = {}
+        self.profile = False
+        return out
+
+    def make_policy(self, prof: Dict[int, dict], cost: CostModel, lossy_ids: Optional[Sequence[int]] = None,
+                    lookahead: int = 2, bwd_factor: float = 2.0, min_bytes: int = 1 << 20) -> List[int]:
+        """Fill `policy` / `begin_stage` from a profiled iteration.
+
+        Tensor id i (the output of layer i) becomes a swap candidate at the
+        first layer that consumes it.  Its swap-out may hide behind the next
+        `lookahead` layers of forward compute and its swap-in behind
+        `bwd_factor` times as much backward compute.  ZFP is allowed on the
+        ids in `lossy_ids` (default: inputs of CONV layers, which is where the
+        reference's drivers apply it, vgg16-cifar10.cpp:381-397)."""
+        n = max(prof) + 1 if prof else 0
+        times = [prof[i]["time_s"] if i in prof else 0.0 for i in range(n)]
+        consumer: Dict[int, int] = {}
+        conv_inputs = set()
+        for idx in sorted(prof):
+            for tid in prof[idx]["inputs"]:
+                if tid >= 0 and tid not in consumer:
+                    consumer[tid] = idx
+                    if prof[idx]["type"] == int(LayerType.CONV):
+                        conv_inputs.add(tid)
+        lossy = set(lossy_ids) if lossy_ids is not None else conv_inputs
+        if len(self.policy) < n:
+            self.policy += [POLICY_KEEP] * (n - len(self.policy))
+            self.begin_stage += [0] * (n - len(self.begin_stage))
+        cands, descs = [], []
+        for tid in sorted(consumer):
+            p = prof.get(tid)
+            if p is None or p["omit"] or not p["float32"] or not p["has_grad"] or p["numel"] * 4 < min_bytes:
+                continue
+            c = consumer[tid]
+            window = sum(times[c:c + lookahead])
+            cands.append(tid)
+            descs.append(TensorDesc(p["numel"], p["zero_fraction"], tid in lossy, window, bwd_factor * window))
+        pol, _ = cost.decide(descs)
+        for tid in range(n):
+            self.policy[tid] = POLICY_KEEP
+        for tid, pcode in zip(cands, pol):
+            self.policy[tid] = pcode
+            self.begin_stage[tid] = consumer[tid]
+        return list(self.policy)

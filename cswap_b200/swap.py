@@ -1,0 +1,196 @@
+"""Python face of the swap manager and cost model (section 4 and 5 of
+include/cswap_b200.h)."""
+from __future__ import annotations
+
+import ctypes as C
+import json
+from dataclasses import dataclass
+from typing import Iterable, List, Optional, Sequence, Tuple
+
+import torch
+
+from ._lib import (CostModelStruct, MgrConfig, MgrStats, TensorDescStruct, TicketInfo, check, lib)
+from .codec import POLICY_RAW, POLICY_SPARSE, POLICY_ZFP, _require_cuda_f32, _stream_ptr
+
+
+class Ticket:
+    """One swapped-out tensor.  Holds the handle and what is needed to
+    rebuild the tensor (shape, device)."""
+
+    __slots__ = ("_mgr", "_h", "shape", "numel", "device", "__weakref__")
+
+    def __init__(self, mgr: "SwapManager", handle: int, shape, numel: int, device):
+        self._mgr, self._h, self.shape, self.numel, self.device = mgr, handle, tuple(shape), numel, device
+
+    @property
+    def alive(self) -> bool:
+        return self._h is not None
+
+    def info(self) -> dict:
+        ti = TicketInfo()
+        check(lib().csw_ticket_query(self._mgr._h, self._h, C.byref(ti)), "csw_ticket_query")
+        return {"policy": ti.policy, "numel": ti.numel, "raw_bytes": ti.raw_bytes, "moved_bytes": ti.moved_bytes,
+                "complete": bool(ti.complete)}
+
+    def release(self) -> None:
+        if self._h is not None and self._mgr._h is not None:
+            check(lib().csw_ticket_release(self._mgr._h, self._h), "csw_ticket_release")  # waits for its copies
+        self._h = None
+        if self._mgr is not None and self._mgr._reading:
+            self._mgr._reading = [(tk, t) for tk, t in self._mgr._reading if tk is not self]
+
+    def __del__(self):
+        try:
+            self.release()
+        except Exception:
+            pass
+
+
+class SwapManager:
+    """One per device / replica: pinned pool, staging pool, codec/D2H/H2D streams."""
+
+    def __init__(self, device: Optional[int] = None, pinned_bytes: int = 0, staging_bytes: int = 0,
+                 zfp_maxbits: int = 512):
+        if device is None:
+            device = torch.cuda.current_device()
+        self.device = torch.device("cuda", int(device))
+        cfg = MgrConfig(int(device), pinned_bytes, staging_bytes, zfp_maxbits)
+        h = C.c_void_p()
+        with torch.cuda.device(self.device):
+            check(lib().csw_mgr_create(C.byref(cfg), C.byref(h)), "csw_mgr_create")
+        self._h = h.value
+        self.zfp_maxbits = zfp_maxbits
+        # Source tensors of swap-outs still being read by the manager's streams.
+        # Holding a reference keeps torch's caching allocator from handing the
+        # block to someone else; it is dropped at the first call after the
+        # device has finished reading.
+        self._reading: List[Tuple[Ticket, torch.Tensor]] = []
+
+    def close(self) -> None:
+        if self._h is not None:
+            check(lib().csw_mgr_destroy(self._h), "csw_mgr_destroy")  # drains the manager's streams
+            self._h = None
+            self._reading.clear()
+
+    def _poll(self) -> None:
+        if self._reading:
+            self._reading = [(tk, t) for tk, t in self._reading if tk._h is not None and not self.out_done(tk)]
+
+    def raw_streams(self) -> Tuple[int, int, int]:
+        """(codec, d2h, h2d) cudaStream_t handles of the manager."""
+        a, b, c = C.c_void_p(), C.c_void_p(), C.c_void_p()
+        check(lib().csw_mgr_get_streams(self._h, C.byref(a), C.byref(b), C.byref(c)), "csw_mgr_get_streams")
+        return a.value, b.value, c.value
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def set_zfp_maxbits(self, maxbits: int) -> None:
+        """The reference's setRatio (CSWAP+/Execution.h:63): bits per zfp block."""
+        check(lib().csw_mgr_set_zfp_maxbits(self._h, maxbits), "csw_mgr_set_zfp_maxbits")
+        self.zfp_maxbits = maxbits
+
+    def swap_out(self, t: torch.Tensor, policy: int) -> Ticket:
+        _require_cuda_f32(t, "t")
+        h = C.c_void_p()
+        check(lib().csw_swap_out(self._h, t.data_ptr(), t.numel(), policy, _stream_ptr(t.device), C.byref(h)),
+              "csw_swap_out")
+        tk = Ticket(self, h.value, t.shape, t.numel(), t.device)
+        self._poll()
+        self._reading.append((tk, t))
+        return tk
+
+    def out_done(self, ticket: Ticket) -> bool:
+        d = C.c_int()
+        check(lib().csw_swap_out_done(self._h, ticket._h, C.byref(d)), "csw_swap_out_done")
+        return bool(d.value)
+
+    def out_wait(self, ticket: Ticket, stream: Optional[torch.cuda.Stream] = None) -> None:
+        s = stream.cuda_stream if stream is not None else _stream_ptr(self.device)
+        check(lib().csw_swap_out_wait(self._h, ticket._h, s), "csw_swap_out_wait")
+
+    def prefetch(self, ticket: Ticket) -> None:
+        check(lib().csw_prefetch(self._h, ticket._h), "csw_prefetch")
+
+    def swap_in(self, ticket: Ticket, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if out is None:
+            out = torch.empty(ticket.shape, dtype=torch.float32, device=ticket.device)
+        _require_cuda_f32(out, "out")
+        if out.numel() != ticket.numel:
+            raise ValueError("out has the wrong number of elements")
+        check(lib().csw_swap_in(self._h, ticket._h, out.data_ptr(), _stream_ptr(out.device)), "csw_swap_in")
+        self._poll()
+        return out
+
+    def stats(self) -> dict:
+        s = MgrStats()
+        check(lib().csw_mgr_get_stats(self._h, C.byref(s)), "csw_mgr_get_stats")
+        return {n: getattr(s, n) for n, _ in MgrStats._fields_}
+
+    def reset_stats(self) -> None:
+        check(lib().csw_mgr_reset_stats(self._h), "csw_mgr_reset_stats")
+
+    def sync(self) -> None:
+        check(lib().csw_mgr_sync(self._h), "csw_mgr_sync")
+
+
+@dataclass
+class TensorDesc:
+    numel: int
+    zero_fraction: float = -1.0
+    lossy_ok: bool = False
+    overlap_fwd_s: float = 0.0
+    overlap_bwd_s: float = 0.0
+
+
+_COST_FIELDS = [n for n, _ in CostModelStruct._fields_]
+
+
+class CostModel:
+    """Fitted linear time models of the codecs and the host link, and the
+    per-tensor decision raw / sparse / ZFP."""
+
+    def __init__(self, **coeffs):
+        self.c = CostModelStruct()
+        for k, v in coeffs.items():
+            if k not in _COST_FIELDS:
+                raise KeyError(k)
+            setattr(self.c, k, v)
+
+    @classmethod
+    def fit(cls, mgr: SwapManager, zfp_maxbits: Optional[int] = None) -> "CostModel":
+        m = cls()
+        m.c.zfp_maxbits = zfp_maxbits or mgr.zfp_maxbits
+        with torch.cuda.device(mgr.device):
+            check(lib().csw_cost_fit(mgr._h, C.byref(m.c)), "csw_cost_fit")
+        return m
+
+    def decide(self, tensors: Sequence[TensorDesc]) -> Tuple[List[int], List[float]]:
+        n = len(tensors)
+        arr = (TensorDescStruct * max(n, 1))()
+        for i, t in enumerate(tensors):
+            arr[i] = TensorDescStruct(t.numel, t.zero_fraction, int(t.lossy_ok), t.overlap_fwd_s, t.overlap_bwd_s)
+        pol = (C.c_int * max(n, 1))()
+        exp = (C.c_double * max(n, 1))()
+        check(lib().csw_cost_decide(C.byref(self.c), arr, n, pol, exp), "csw_cost_decide")
+        return list(pol[:n]), list(exp[:n])
+
+    def as_dict(self) -> dict:
+        return {k: getattr(self.c, k) for k in _COST_FIELDS}
+
+    def save(self, path: str, policy: Optional[Iterable[int]] = None) -> None:
+        """Persist the coefficients (and optionally the chosen policy vector)."""
+        with open(path, "w") as f:
+            json.dump({"cost_model": self.as_dict(), "policy": list(policy) if policy is not None else None}, f,
+                      indent=1)
+
+    @classmethod
+    def load(cls, path: str) -> Tuple["CostModel", Optional[List[int]]]:
+        with open(path) as f:
+            d = json.load(f)
+        if not isinstance(d, dict) or "cost_model" not in d:
+            raise ValueError(f"{path}: not a cost-model file")
+        return cls(**d["cost_model"]), d.get("policy")

@@ -141,6 +141,17 @@ static int max_exponent(const float* p, int n) {
   return e;
 }
 
+/* (int32) conversion of encode.cuh:147 with the semantics the GPU gives it
+ * (cvt.rzi.s32.f32): truncation, saturation, NaN -> 0.  Only blocks whose
+ * largest magnitude is below 2^-97 (scale factor overflows, encode.cuh:53)
+ * ever leave the range. */
+static int32_t cast_rz(float p) {
+  if (p != p) return 0;
+  if (p >= 2147483648.0f) return INT32_MAX;
+  if (p <= -2147483648.0f) return INT32_MIN;
+  return (int32_t)p;
+}
+
 /* encode.cuh:306-345 after the transform: embedded group-tested plane coder */
 static int encode_planes(bitcur* c, const uint32_t* u, int size, unsigned budget) {
   unsigned bits = budget, n = 0, k;
@@ -204,7 +215,7 @@ int orc_zfp_encode_block(const float* fblock, int dims, unsigned maxbits, size_t
   int32_t iblock[64];
   uint32_t ublock[64];
   float s = ldexpf(1.0f, 30 - emax); /* encode.cuh:125-131 */
-  for (int i = 0; i < size; i++) iblock[i] = (int32_t)(s * fblock[i]);
+  for (int i = 0; i < size; i++) iblock[i] = cast_rz(s * fblock[i]);
   fwd_xform(iblock, dims);
   const unsigned char* perm = perm_for(dims);
   for (int i = 0; i < size; i++) ublock[i] = orc_int2uint(iblock[perm[i]]);
@@ -237,14 +248,11 @@ static int field_dims(size_t ny, size_t nz) { return nz ? 3 : ny ? 2 : 1; }
 
 size_t orc_zfp_stream_bytes(size_t nx, size_t ny, size_t nz, unsigned maxbits) {
   int d = field_dims(ny, nz);
-  size_t px = (nx + 3) & ~(size_t)3, py = (ny + 3) & ~(size_t)3, pz = (nz + 3) & ~(size_t)3;
-  if (d == 3) { /* shared.h:73-84: truncating division */
-    size_t blocks = px * py * pz / 64;
-    return blocks * maxbits / 64 * 8;
-  }
-  size_t blocks = d == 2 ? (nx * ny + 15) / 16 : (nx + 3) / 4; /* shared.h:39-71 */
-  size_t bits = blocks * maxbits;
-  return (bits + 63) / 64 * 8;
+  size_t bx = (nx + 3) / 4, by = d >= 2 ? (ny + 3) / 4 : 1, bz = d >= 3 ? (nz + 3) / 4 : 1;
+  /* Whole words covering every block.  The reference's own byte counts
+   * (shared.h:39-84) truncate for 3-D and count unpadded values for 1-D/2-D;
+   * they agree with this whenever maxbits % 64 == 0 and no block is partial. */
+  return (bx * by * bz * maxbits + 63) / 64 * 8;
 }
 
 /* encode.cuh:17-38 */

@@ -23,9 +23,9 @@ extern "C" {
 
 /* ---- ZFP fixed-rate float32, 1-D / 2-D / 3-D ---------------------------- */
 
-/* Stream bytes the reference allocates/zeros for a field
- * (shared.h:39-84 calc_device_mem{1,2,3}d): floor(blocks*maxbits/64)*8 for
- * 3-D, ceil for 1-D/2-D.  ny==0 / nz==0 select lower dimensionality. */
+/* Bytes of whole 64-bit words covering every (padded) block of the field.
+ * Equals the reference's shared.h:39-84 counts when maxbits % 64 == 0 and no
+ * block is partial.  ny==0 / nz==0 select lower dimensionality. */
 size_t orc_zfp_stream_bytes(size_t nx, size_t ny, size_t nz, unsigned maxbits);
 
 /* Encode a contiguous float32 array viewed as nx*ny*nz (x fastest) at

@@ -1,0 +1,77 @@
+// Host build of the per-block codec core (cswap_b200/csrc/zfp_core.cuh), used
+// by the CPU test-suite to check the register-level algorithm (byte-sliced
+// plane transposes, table-driven group-test coding) bit for bit against the
+// oracle without a GPU.  Test scaffolding: the shipped library never runs
+// the codec on the host.
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <vector>
+
+#include "../cswap_b200/csrc/zfp_field.cuh"
+
+namespace {
+struct VecSink {
+  uint32_t* w;
+  void put(int i, uint32_t v) { w[i] = v; }
+};
+struct VecSource {
+  const uint32_t* w;
+  int n;
+  uint32_t get(int i) const { return i < n ? w[i] : 0u; }
+};
+std::vector<uint32_t> enc_lut() {
+  std::vector<uint32_t> t(csw::ENC_LUT_SIZE);
+  for (int i = 0; i < csw::ENC_LUT_SIZE; i++) t[i] = csw::enc_lut_entry(i);
+  return t;
+}
+std::vector<uint32_t> dec_lut() {
+  std::vector<uint32_t> t(csw::DEC_LUT_SIZE);
+  for (int i = 0; i < csw::DEC_LUT_SIZE; i++) t[i] = csw::dec_lut_entry(i);
+  return t;
+}
+
+template <int DIMS>
+void encode_field(const csw::FieldGeom& g, const float* in, int maxbits, uint32_t* out) {
+  auto lut = enc_lut();
+  const int nw = maxbits / 32;
+  size_t nb = csw::geom_blocks(g);
+  for (size_t b = 0; b < nb; b++) {
+    float q[1 << (2 * DIMS)];
+    csw::gather_block<DIMS>(g, in, b, q);
+    VecSink s{out + b * nw};
+    csw::encode_block<DIMS>(q, maxbits, s, lut.data());
+  }
+}
+template <int DIMS>
+void decode_field(const csw::FieldGeom& g, const uint32_t* in, int maxbits, float* out) {
+  auto lut = dec_lut();
+  const int nw = maxbits / 32;
+  size_t nb = csw::geom_blocks(g);
+  for (size_t b = 0; b < nb; b++) {
+    float q[1 << (2 * DIMS)];
+    VecSource s{in + b * nw, nw};
+    csw::decode_block<DIMS>(s, maxbits, q, lut.data());
+    csw::scatter_block<DIMS>(g, out, b, q);
+  }
+}
+}  // namespace
+
+extern "C" {
+// maxbits must be a multiple of 32 here (whole words per block)
+void core_encode(const float* in, size_t nx, size_t ny, size_t nz, int maxbits, uint32_t* out) {
+  csw::FieldGeom g = csw::make_geom(nx, ny, nz, 0, 0, 0);
+  if (g.dims == 3) encode_field<3>(g, in, maxbits, out);
+  else if (g.dims == 2) encode_field<2>(g, in, maxbits, out);
+  else encode_field<1>(g, in, maxbits, out);
+}
+void core_decode(const uint32_t* in, size_t nx, size_t ny, size_t nz, int maxbits, float* out) {
+  csw::FieldGeom g = csw::make_geom(nx, ny, nz, 0, 0, 0);
+  if (g.dims == 3) decode_field<3>(g, in, maxbits, out);
+  else if (g.dims == 2) decode_field<2>(g, in, maxbits, out);
+  else decode_field<1>(g, in, maxbits, out);
+}
+size_t core_stream_bytes(size_t nx, size_t ny, size_t nz, unsigned maxbits) {
+  return csw::stream_bytes(csw::make_geom(nx, ny, nz, 0, 0, 0), maxbits);
+}
+}

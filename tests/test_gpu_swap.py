@@ -1,0 +1,259 @@
+"""Swap manager, cost model and the Execution mirror on a GPU."""
+import numpy as np
+import pytest
+
+import util
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def cs():
+    import torch
+    import cswap_b200
+    assert torch.cuda.is_available()
+    cswap_b200.lib()
+    return cswap_b200
+
+
+@pytest.fixture()
+def mgr(cs):
+    m = cs.SwapManager(pinned_bytes=256 << 20, staging_bytes=128 << 20)
+    yield m
+    m.close()
+
+
+def test_raw_roundtrip(cs, mgr):
+    import torch
+    t = torch.from_numpy(util.normal(1 << 20, 1)).cuda()
+    tk = mgr.swap_out(t, cs.POLICY_RAW)
+    back = mgr.swap_in(tk)
+    torch.cuda.synchronize()
+    assert torch.equal(back, t)
+    info = tk.info()
+    assert info["policy"] == cs.POLICY_RAW and info["moved_bytes"] == 4 << 20 and info["complete"]
+    tk.release()
+    s = mgr.stats()
+    assert s["swap_outs"] == 1 and s["swap_ins"] == 1 and s["pinned_in_use"] == 0 and s["staging_in_use"] == 0
+
+
+def test_zfp_matches_codec(cs, mgr):
+    import torch
+    t = torch.from_numpy(util.tanh_normal(4 << 20, 2)).cuda()
+    want = cs.zfp_decompress(cs.zfp_compress(t, 512), t.numel(), 512)
+    tk = mgr.swap_out(t, cs.POLICY_ZFP)
+    mgr.sync()
+    assert mgr.out_done(tk)
+    back = mgr.swap_in(tk)
+    torch.cuda.synchronize()
+    assert torch.equal(back, want)
+    assert tk.info()["moved_bytes"] == t.numel()  # rate 8: one byte per value
+    tk.release()
+
+
+def test_sparse_exact_and_sized(cs, mgr):
+    import torch
+    a = util.relu_normal(4 << 20, 0.75, 3)
+    a[::9] = -0.0
+    t = torch.from_numpy(a).cuda()
+    tk = mgr.swap_out(t, cs.POLICY_SPARSE)
+    back = mgr.swap_in(tk)
+    torch.cuda.synchronize()
+    assert torch.equal(back.view(torch.int32), t.view(torch.int32))
+    info = tk.info()
+    nnz = int(torch.count_nonzero(t.view(torch.int32)).item())
+    assert info["complete"] and info["moved_bytes"] == cs.sparse_packed_bytes(t.numel(), nnz)
+    tk.release()
+    assert mgr.stats()["pinned_in_use"] == 0
+
+
+def test_zfp_falls_back_to_raw_for_odd_sizes(cs, mgr):
+    import torch
+    t = torch.from_numpy(util.normal(1000, 4)).cuda()
+    tk = mgr.swap_out(t, cs.POLICY_ZFP)
+    assert tk.info()["policy"] == cs.POLICY_RAW
+    assert torch.equal(mgr.swap_in(tk), t)
+    tk.release()
+
+
+def test_many_tensors_interleaved_with_compute(cs, mgr):
+    """Swap-outs overlap later compute; swap-ins come back in reverse order with prefetch."""
+    import torch
+    xs, tks = [], []
+    w = torch.randn(512, 512, device="cuda")
+    for i in range(12):
+        x = torch.relu(torch.randn(1 << 20, device="cuda") - 0.5)
+        pol = [cs.POLICY_RAW, cs.POLICY_SPARSE, cs.POLICY_ZFP][i % 3]
+        tks.append(mgr.swap_out(x, pol))
+        xs.append(x.clone() if pol != cs.POLICY_ZFP else cs.zfp_decompress(cs.zfp_compress(x, 512), x.numel(), 512))
+        del x
+        w = w @ w.t() * 1e-3  # unrelated compute on the main stream
+    for i in reversed(range(12)):
+        if i > 0:
+            mgr.prefetch(tks[i - 1])
+        back = mgr.swap_in(tks[i])
+        assert torch.equal(back.view(torch.int32), xs[i].view(torch.int32)), i
+        tks[i].release()
+    s = mgr.stats()
+    assert s["swap_outs"] == 12 and s["swap_ins"] == 12
+    assert s["moved_bytes_out"] < s["raw_bytes_out"]
+    assert s["pinned_in_use"] == 0 and s["staging_in_use"] == 0
+
+
+def test_pool_exhaustion_reports_nomem(cs):
+    import torch
+    m = cs.SwapManager(pinned_bytes=1 << 20, staging_bytes=1 << 20)
+    t = torch.zeros(1 << 20, device="cuda")  # 4 MiB > pool
+    with pytest.raises(cs.CswapError) as e:
+        m.swap_out(t, cs.POLICY_RAW)
+    assert e.value.status == 4
+    small = torch.ones(1 << 16, device="cuda")
+    tk = m.swap_out(small, cs.POLICY_RAW)  # the manager is still usable
+    assert torch.equal(m.swap_in(tk), small)
+    tk.release()
+    m.close()
+
+
+def test_cost_model_fit_and_decide(cs, mgr, tmp_path):
+    cm = cs.CostModel.fit(mgr)
+    d = cm.as_dict()
+    assert d["d2h_bps"] > 1e9 and d["h2d_bps"] > 1e9
+    assert d["zfp_enc_b"] > 0 and d["sparse_enc_b"] > 0
+    n = 8 << 20
+    big_window, no_window = 1.0, 0.0
+    pol, exp = cm.decide([
+        cs.TensorDesc(n, zero_fraction=0.9, lossy_ok=False, overlap_fwd_s=no_window, overlap_bwd_s=no_window),
+        cs.TensorDesc(n, zero_fraction=0.0, lossy_ok=True, overlap_fwd_s=no_window, overlap_bwd_s=no_window),
+        cs.TensorDesc(n, zero_fraction=0.0, lossy_ok=False, overlap_fwd_s=no_window, overlap_bwd_s=no_window),
+        cs.TensorDesc(n, zero_fraction=0.9, lossy_ok=True, overlap_fwd_s=big_window, overlap_bwd_s=big_window),
+        cs.TensorDesc(1000, zero_fraction=0.0, lossy_ok=True),
+    ])
+    assert pol[0] == cs.POLICY_SPARSE       # very sparse, lossless only
+    assert pol[1] == cs.POLICY_ZFP          # dense, loss allowed, nothing to hide behind
+    assert pol[2] == cs.POLICY_RAW          # dense and lossless: nothing helps
+    assert pol[3] == cs.POLICY_RAW          # everything hides behind compute: keep it simple
+    assert pol[4] == cs.POLICY_RAW          # not a multiple of 1024: ZFP not applicable
+    path = tmp_path / "policy.json"
+    cm.save(str(path), pol)
+    cm2, pol2 = cs.CostModel.load(str(path))
+    assert pol2 == pol and cm2.as_dict() == d
+    path.write_text("{ truncated")
+    with pytest.raises(Exception):
+        cs.CostModel.load(str(path))
+
+
+def _small_net(torch):
+    torch.manual_seed(0)
+    import torch.nn as nn
+    layers = [nn.Conv2d(3, 32, 3, padding=1), nn.ReLU(), nn.Conv2d(32, 32, 3, padding=1), nn.ReLU(),
+              nn.MaxPool2d(2), nn.Conv2d(32, 64, 3, padding=1), nn.ReLU(), nn.Flatten(), nn.Linear(64 * 16 * 16, 10)]
+    return nn.Sequential(*layers).cuda()
+
+
+def _step(cs, torch, net, x, y, policy_for):
+    """One forward/backward with every layer wrapped in pre/post; returns loss and grads."""
+    exe = cs.Execution()
+    n = len(net)
+    exe.init_(n + 1)
+    for i in range(n):
+        exe.begin_stage[i] = i + 1
+        exe.policy[i] = policy_for(i, net[i])
+    for p in net.parameters():
+        p.grad = None
+    exe.preforward()
+    h = x
+    for i, layer in enumerate(net):
+        lt = cs.LayerType.CONV if isinstance(layer, torch.nn.Conv2d) else cs.LayerType.ACT
+        exe.pre(h, lt)
+        out = layer(h)
+        exe.post(h, out, lt)
+        h = out
+    exe.postforward()
+    loss = torch.nn.functional.cross_entropy(h, y)
+    loss.backward()
+    torch.cuda.synchronize()
+    grads = [p.grad.clone() for p in net.parameters()]
+    stats = exe.mgr.stats()
+    exe.mgr.close()
+    return float(loss.detach()), grads, stats, exe
+
+
+def test_execution_lossless_policies_do_not_change_training(cs):
+    import torch
+    net = _small_net(torch)
+    x = torch.randn(64, 3, 32, 32, device="cuda")
+    y = torch.randint(0, 10, (64,), device="cuda")
+    torch.backends.cudnn.deterministic = True
+    base_loss, base_grads, _, _ = _step(cs, torch, net, x, y, lambda i, l: cs.POLICY_KEEP)
+    for pol in (cs.POLICY_RAW, cs.POLICY_SPARSE):
+        loss, grads, stats, exe = _step(cs, torch, net, x, y, lambda i, l: pol)
+        assert exe.swapped_tensors >= 6 and stats["swap_ins"] >= 4  # not every swapped tensor is needed again
+        assert loss == base_loss
+        for g, b in zip(grads, base_grads):
+            assert torch.equal(g, b)
+    # sparse moves fewer bytes than raw on the ReLU outputs
+    _, _, s_raw, _ = _step(cs, torch, net, x, y, lambda i, l: cs.POLICY_RAW if isinstance(l, torch.nn.ReLU) else 0)
+    _, _, s_sp, _ = _step(cs, torch, net, x, y, lambda i, l: cs.POLICY_SPARSE if isinstance(l, torch.nn.ReLU) else 0)
+    assert s_sp["moved_bytes_out"] < 0.8 * s_raw["moved_bytes_out"]
+
+
+def test_execution_zfp_equals_codec_applied_to_activations(cs):
+    """With policy 6 on one tensor, backward sees exactly decode(encode(x))."""
+    import torch
+    torch.manual_seed(1)
+    lin = torch.nn.Linear(1024, 1024).cuda()
+    x0 = torch.randn(256, 1024, device="cuda", requires_grad=True)
+    h = torch.tanh(x0)  # id 0
+    exe = cs.Execution()
+    exe.init_(4)
+    exe.policy[0] = cs.POLICY_ZFP
+    exe.begin_stage[0] = 1
+    exe.preforward()
+    exe.pre(x0)
+    h = torch.tanh(x0)
+    exe.post(x0, h)          # h.tensor_id = 0
+    exe.pre(h)               # index 1 == begin_stage[0] -> swap h out with ZFP
+    out = lin(h)
+    exe.post(h, out)
+    exe.postforward()
+    h_ref = h.detach().clone()
+    del h
+    out.sum().backward()
+    torch.cuda.synchronize()
+    lossy = cs.zfp_decompress(cs.zfp_compress(h_ref.view(-1), 512), h_ref.numel(), 512).view_as(h_ref)
+    # dL/dW = ones^T @ h : computed from the decompressed activation
+    want = torch.ones(256, 1024, device="cuda").t() @ lossy
+    assert torch.allclose(lin.weight.grad, want, rtol=1e-5, atol=1e-4)
+    assert not torch.allclose(lossy, h_ref)  # the activation really went through the lossy codec
+    # tanh's own backward used the same record (1 - h^2 with the lossy h)
+    want_x = (torch.ones(256, 1024, device="cuda") @ lin.weight.detach()) * (1 - lossy * lossy)
+    assert torch.allclose(x0.grad, want_x, rtol=1e-4, atol=1e-5)
+    assert exe.mgr.stats()["swap_ins"] == 1
+    exe.mgr.close()
+
+
+def test_profile_and_make_policy(cs):
+    import torch
+    net = _small_net(torch)
+    x = torch.randn(128, 3, 32, 32, device="cuda")
+    exe = cs.Execution(mgr=cs.SwapManager(pinned_bytes=512 << 20, staging_bytes=128 << 20))
+    exe.init_(len(net) + 1)
+    exe.profile = True
+    exe.preforward()
+    h = x.requires_grad_()
+    for i, layer in enumerate(net):
+        lt = cs.LayerType.CONV if isinstance(layer, torch.nn.Conv2d) else cs.LayerType.ACT
+        exe.pre(h, lt)
+        out = layer(h)
+        exe.post(h, out, lt)
+        h = out
+    exe.postforward()
+    prof = exe.finish_profile()
+    assert len(prof) == len(net) and all(p["time_s"] >= 0 for p in prof.values())
+    assert 0.3 < prof[1]["zero_fraction"] < 0.7  # first ReLU output
+    cm = cs.CostModel.fit(exe.mgr)
+    pol = exe.make_policy(prof, cm, min_bytes=1 << 16)
+    assert len(pol) >= len(net)
+    assert set(pol) <= {0, 2, 3, 6}
+    assert exe.begin_stage[1] == 2  # ReLU output is consumed by the next conv
+    exe.mgr.close()
