@@ -331,77 +331,128 @@ CSW_HD uint32_t dec_lut_entry(int idx) {
 
 // ---- bit emitter ------------------------------------------------------------------
 // WordSink::put(w, word) receives the block's w-th 32-bit stream word; words
-// arrive in increasing w, each once.
+// arrive in increasing w, each once.  Everything is written for predication
+// rather than branches: lanes of a warp code different blocks and would
+// otherwise diverge on every word boundary.
+CSW_HD uint32_t funnel_l(uint32_t lo, uint32_t hi, int s) {  // ((hi:lo) << s) >> 32, s in 0..31
+#if defined(__CUDA_ARCH__)
+  return __funnelshift_l(lo, hi, s);
+#else
+  return (uint32_t)(((((uint64_t)hi << 32) | lo) << (s & 31)) >> 32);
+#endif
+}
+CSW_HD uint32_t funnel_r(uint32_t lo, uint32_t hi, int s) {  // low word of (hi:lo) >> s, s in 0..31
+#if defined(__CUDA_ARCH__)
+  return __funnelshift_r(lo, hi, s);
+#else
+  return (uint32_t)((((uint64_t)hi << 32) | lo) >> (s & 31));
+#endif
+}
+
 template <class WordSink>
 struct Emitter {
-  uint64_t acc;
-  int fill;   // valid bits in acc, < 32 between calls
-  int wpos;   // words already handed to the sink
-  int nwords; // ceil(maxbits / 32)
+  uint32_t a0;  // the word being filled; bits at and above `fill` are zero
+  int fill;     // 0..31
+  int wpos;     // words already handed to the sink
+  int nwords;   // ceil(maxbits / 32)
   WordSink& sink;
-  CSW_HD Emitter(WordSink& s, int nw) : acc(0), fill(0), wpos(0), nwords(nw), sink(s) {}
+  CSW_HD Emitter(WordSink& s, int nw) : a0(0), fill(0), wpos(0), nwords(nw), sink(s) {}
   CSW_HD int total() const { return 32 * wpos + fill; }
-  // append the low `len` (0..32) bits of v; bits of v above len must be zero
-  CSW_HD void emit(uint32_t v, int len) {
-    acc |= (uint64_t)v << fill;
-    fill += len;
-    if (fill >= 32) {
-      if (wpos < nwords) sink.put(wpos, (uint32_t)acc);
-      wpos++;
-      acc >>= 32;
-      fill -= 32;
+  CSW_HD void flush_word(uint32_t next) {
+    if (wpos < nwords) sink.put(wpos, a0);
+    wpos++;
+    a0 = next;
+  }
+  // append the low `len` (0..32) bits of v; bits of v at and above len must be zero
+  CSW_HD void emit32(uint32_t v, int len) {
+    const uint32_t t1 = funnel_l(v, 0u, fill);
+    a0 |= v << fill;
+    int nf = fill + len;
+    if (nf >= 32) {
+      flush_word(t1);
+      nf -= 32;
     }
+    fill = nf;
+  }
+  // append the low `len` (0..64) bits of hi:lo; bits at and above len must be zero
+  CSW_HD void emit64(uint32_t lo, uint32_t hi, int len) {
+    uint32_t t1 = funnel_l(lo, hi, fill);
+    const uint32_t t2 = funnel_l(hi, 0u, fill);
+    a0 |= lo << fill;
+    int nf = fill + len;
+    if (nf >= 32) {
+      flush_word(t1);
+      t1 = t2;
+      nf -= 32;
+    }
+    if (nf >= 32) {
+      flush_word(t1);
+      nf -= 32;
+    }
+    fill = nf;
   }
   // hand over whatever is buffered and zero-fill the rest of the block
   CSW_HD void finish() {
-    while (wpos < nwords) {
-      sink.put(wpos, (uint32_t)acc);
-      acc >>= 32;
-      wpos++;
-    }
+    while (wpos < nwords) flush_word(0u);
+  }
+};
+
+// ---- encoder: coefficient-count state ----------------------------------------------
+// n coefficients are significant so far; the masks select plane bits below n
+// and the single bit at position n (zero when n == 64).
+struct SigState {
+  int n;
+  uint32_t mlo, mhi;  // low n bits of a 64-bit plane word
+  uint32_t glo, ghi;  // bit n
+  CSW_HD void set(int nn) {
+    n = nn;
+    mlo = nn >= 32 ? 0xffffffffu : ((1u << nn) - 1u);
+    mhi = nn <= 32 ? 0u : low_mask32(nn - 32);
+    glo = nn < 32 ? (1u << nn) : 0u;
+    ghi = (nn >= 32 && nn < 64) ? (1u << (nn - 32)) : 0u;
   }
 };
 
 // ---- encoder: one plane -----------------------------------------------------------
-// Codes plane word x (coefficient i at bit i, N coefficients) given n already
-// significant coefficients (encode.cuh:336-343).  Emission ignores the bit
-// budget: the stream is an exact prefix of the unlimited-budget stream, so the
-// caller stops once total() reaches maxbits and the emitter drops the overrun.
+// Codes plane word hi:lo (coefficient i at bit i, N coefficients) given the
+// significance state (encode.cuh:336-343).  Emission ignores the bit budget:
+// the stream is an exact prefix of the unlimited-budget stream, so the caller
+// stops once total() reaches maxbits and the emitter drops the overrun.
+//
+// The first group-test bit rides on the verbatim prefix (it is bit n of the
+// same word).  The rest of the group-test phase is produced eight positions
+// per step from enc_lut; the loop body has no branches, so lanes only differ
+// in how many steps they take.
 template <int N, class WordSink>
-CSW_HD void encode_plane(uint64_t x, int& n, Emitter<WordSink>& em, const uint32_t* enc_lut) {
-  // step 2: first n bits verbatim
-  if (n > 0) {
-    if (n <= 32) {
-      em.emit((uint32_t)x & low_mask32(n), n);
-    } else {
-      em.emit((uint32_t)x, 32);
-      em.emit((uint32_t)(x >> 32) & low_mask32(n - 32), n - 32);
-    }
-  }
-  if (n >= N) return;
-  // step 3: group tests + unary runs over the remaining positions
-  uint64_t xs = x >> n;
-  if (xs == 0) {
-    em.emit(0u, 1);
+CSW_HD void encode_plane(uint32_t lo, uint32_t hi, SigState& sg, Emitter<WordSink>& em, const uint32_t* enc_lut) {
+  if (sg.n >= N) {  // everything significant: the plane is copied verbatim
+    em.emit64(lo, hi, N);
     return;
   }
-  em.emit(1u, 1);
-  const int top = (int)((x >> (N - 1)) & 1u);  // last position set: its 1 is implied
-  for (;;) {
-    uint32_t e = enc_lut[(uint32_t)xs & 0xffu];
-    xs >>= 8;
-    if (xs != 0) {
-      em.emit(e & 0xffffu, (int)((e >> 16) & 0x1fu));
-    } else {
-      int lf = (int)(e >> 24);
-      // drop the '0' terminator slot from the pattern; when the plane ends on
-      // the last position neither its 1 nor a terminator is coded
-      em.emit(e & 0xffffu & low_mask32(lf - 1 - top), lf - 2 * top);
-      break;
-    }
-  }
-  int msb = 64 - clz64(x);
-  n = n > msb ? n : msb;
+  // remaining positions xs = x >> n (n < 64)
+  const int n = sg.n, s = n & 31;
+  const uint32_t fl = funnel_r(lo, hi, s), sh = hi >> s;
+  uint32_t xl = n < 32 ? fl : sh;
+  uint32_t xh = n < 32 ? sh : 0u;
+  const bool any = (xl | xh) != 0u;
+  em.emit64((lo & sg.mlo) | (any ? sg.glo : 0u), (hi & sg.mhi) | (any ? sg.ghi : 0u), n + 1);
+  if (!any) return;
+  const int top = (int)((N == 64 ? hi >> 31 : lo >> (N - 1)) & 1u);  // last position set: its 1 is implied
+  bool more;
+  do {
+    const uint32_t e = enc_lut[xl & 0xffu];
+    xl = funnel_r(xl, xh, 8);
+    xh >>= 8;
+    more = (xl | xh) != 0u;
+    // a byte that holds the plane's last set bit ends with the '0' terminator
+    // (dropped from the pattern) or, on the last position, with nothing at all
+    const int lf = (int)(e >> 24);
+    const int len = more ? (int)((e >> 16) & 0x1fu) : lf - 2 * top;
+    const uint32_t keep = more ? 0xffffu : low_mask32(lf - 1 - top);
+    em.emit32(e & keep, len);
+  } while (more);
+  const int msb = hi ? 64 - clz32(hi) : 32 - clz32(lo);
+  sg.set(msb);  // xs != 0, so the top set bit lies at or above n
 }
 
 // ---- encoder: whole block ---------------------------------------------------------
@@ -420,7 +471,7 @@ CSW_HD void encode_block(const float (&f)[1 << (2 * DIMS)], int maxbits, WordSin
     em.finish();
     return;
   }
-  em.emit((2u * e + 1u) & 0x1ffu, 9);
+  em.emit32((2u * e + 1u) & 0x1ffu, 9);
   int v[N];
   {
     const float s = quant_scale(e);
@@ -431,19 +482,21 @@ CSW_HD void encode_block(const float (&f)[1 << (2 * DIMS)], int maxbits, WordSin
   uint32_t u[N];
   fwd_order<DIMS>(v, u, std::make_integer_sequence<int, N>{});
 
-  int n = 0;
+  SigState sg;
+  sg.set(0);
   for (int c = 3; c >= 0; c--) {  // planes 8c+7 .. 8c
     const uint32_t sel = (uint32_t)c | ((uint32_t)(4 + c) << 4);
     uint32_t lo[8], hi[8];
     planes_of_byte<0>(u, sel, lo);
-    if constexpr (N == 64) planes_of_byte<1>(u, sel, hi);
+    if constexpr (N == 64) {
+      planes_of_byte<1>(u, sel, hi);
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; k++) hi[k] = 0u;
+    }
 #pragma unroll
     for (int k = 7; k >= 0; k--) {
-      if (em.total() < maxbits) {
-        uint64_t x = lo[k];
-        if constexpr (N == 64) x |= (uint64_t)hi[k] << 32;
-        encode_plane<N>(x, n, em, enc_lut);
-      }
+      if (em.total() < maxbits) encode_plane<N>(lo[k], hi[k], sg, em, enc_lut);
     }
     if (em.total() >= maxbits) break;
   }
