@@ -88,6 +88,14 @@ CSW_HD int f2i_rz(float f) {
   return (int)f;
 #endif
 }
+// true when the predicate holds on every active lane of the warp (host: the one "lane")
+CSW_HD bool warp_all(bool p) {
+#if defined(__CUDA_ARCH__)
+  return __all_sync(__activemask(), p);
+#else
+  return p;
+#endif
+}
 CSW_HD uint32_t low_mask32(int n) {  // n in 0..32
   return n >= 32 ? 0xffffffffu : ((1u << n) - 1u);
 }
@@ -501,6 +509,210 @@ CSW_HD void encode_block(const float (&f)[1 << (2 * DIMS)], int maxbits, WordSin
     if (em.total() >= maxbits) break;
   }
   em.finish();
+}
+
+// ---- staged encoder (3-D blocks, whole words per block) ----------------------------
+// Same stream as encode_block, produced in a way that suits a warp whose lanes
+// code 32 different blocks:
+//
+//  * every plane's bit offset is known before its bits are made: a plane costs
+//    n verbatim bits, one group-test bit and, when new coefficients turn
+//    significant in it, (top - n) value bits + one group-test bit per set bit
+//    (minus the implied final 1 and its terminator when the plane ends on the
+//    last position).  So the verbatim parts are OR-ed into the staged words at
+//    their offsets, one plane after the other, by all lanes in step;
+//  * the expansions (the data-dependent part) are queued per lane and worked off
+//    in one flat loop per eight planes, each lane running through its own queue,
+//    so lanes do not wait for each other plane by plane.
+//
+// On sm_100 shifts, logic and compares issue on the integer ALU pipe at half
+// the warp rate while integer multiply-adds go down the (otherwise idle)
+// multiply-add pipe at the same rate.  Additions and left shifts are therefore
+// written as multiply-adds with multipliers the compiler cannot see (they come
+// in as kernel arguments), which moves about half of the lifting and transpose
+// work off the ALU pipe.
+struct PipeConsts {
+  int one, mone;         // 1, -1
+  uint32_t p1, p2, p4;   // 1 << 1, 1 << 2, 1 << 4
+};
+CSW_HD PipeConsts pipe_consts() { return PipeConsts{1, -1, 2u, 4u, 16u}; }
+
+CSW_HD int imad(int a, int b, int c) {
+#if defined(__CUDA_ARCH__)
+  int d;
+  asm("mad.lo.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+#else
+  return (int)((uint32_t)a * (uint32_t)b + (uint32_t)c);
+#endif
+}
+CSW_HD uint32_t umad(uint32_t a, uint32_t b, uint32_t c) { return (uint32_t)imad((int)a, (int)b, (int)c); }
+
+// fwd_lift with eight of its ten additions on the multiply-add pipe
+CSW_HD void fwd_lift_bal(int& x, int& y, int& z, int& w, const PipeConsts& k) {
+  x = imad(x, k.one, w); x >>= 1; w = imad(x, k.mone, w);
+  z = imad(z, k.one, y); z >>= 1; y = imad(z, k.mone, y);
+  x = imad(x, k.one, z); x >>= 1; z = imad(x, k.mone, z);
+  w = imad(w, k.one, y); w >>= 1; y = imad(w, k.mone, y);
+  w = wadd(w, y >> 1); y = wsub(y, w >> 1);
+}
+CSW_HD void fwd_xform3_bal(int (&v)[64], const PipeConsts& k) {
+#pragma unroll
+  for (int i = 0; i < 16; i++) fwd_lift_bal(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3], k);
+#pragma unroll
+  for (int z = 0; z < 4; z++)
+#pragma unroll
+    for (int x = 0; x < 4; x++)
+      fwd_lift_bal(v[16 * z + x], v[16 * z + x + 4], v[16 * z + x + 8], v[16 * z + x + 12], k);
+#pragma unroll
+  for (int i = 0; i < 16; i++) fwd_lift_bal(v[i], v[i + 16], v[i + 32], v[i + 48], k);
+}
+
+template <int S, uint32_t M>
+CSW_HD void tswap_bal(uint32_t& a, uint32_t& b, uint32_t pow) {  // pow = 1 << S
+  const uint32_t bs = umad(b, pow, 0u);
+  const uint32_t na = (a & M) | (bs & ~M);
+  const uint32_t nb = ((a >> S) & M) | (b & ~M);
+  a = na;
+  b = nb;
+}
+CSW_HD void transpose8_bal(uint32_t (&r)[8], const PipeConsts& k) {
+#pragma unroll
+  for (int j = 0; j < 4; j++) tswap_bal<4, 0x0f0f0f0fu>(r[j], r[j + 4], k.p4);
+#pragma unroll
+  for (int j = 0; j < 8; j += 4) {
+    tswap_bal<2, 0x33333333u>(r[j], r[j + 2], k.p2);
+    tswap_bal<2, 0x33333333u>(r[j + 1], r[j + 3], k.p2);
+  }
+#pragma unroll
+  for (int j = 0; j < 8; j += 2) tswap_bal<1, 0x55555555u>(r[j], r[j + 1], k.p1);
+}
+template <int G>
+CSW_HD void planes_of_byte_bal(const uint32_t (&u)[64], uint32_t sel, uint32_t (&p)[8], const PipeConsts& k) {
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const uint32_t t0 = byte_perm(u[32 * G + j], u[32 * G + 8 + j], sel);
+    const uint32_t t1 = byte_perm(u[32 * G + 16 + j], u[32 * G + 24 + j], sel);
+    p[j] = byte_perm(t0, t1, 0x5410);
+  }
+  transpose8_bal(p, k);
+}
+
+constexpr int STAGE_SPARE_ROWS = 2;  // words a write may run past the block's last word
+constexpr int QUEUE_SLOTS = 8;       // expansions per lane per eight planes
+constexpr int QUEUE_FIELDS = 3;
+
+// Stage: or_word(w, v) ORs v into the block's w-th staged word (rows
+// 0 .. nwords + STAGE_SPARE_ROWS - 1 exist and rows below nwords start as 0);
+// q_put / q_get access the lane's expansion queue.
+template <class Stage>
+CSW_HD void stage_put64(Stage& st, int off, uint32_t lo, uint32_t hi) {
+  const int s = off & 31, w = off >> 5;
+  st.or_word(w, lo << s);
+  st.or_word(w + 1, funnel_l(lo, hi, s));
+  st.or_word(w + 2, funnel_l(hi, 0u, s));
+}
+
+template <class Stage>
+CSW_HD void encode_block3_staged(const float (&f)[64], int maxbits, Stage& st, const uint32_t* enc_lut,
+                                 const PipeConsts& kc) {
+  float m = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 64; i++) m = fmaxf(m, fabsf(f[i]));
+  const uint32_t e = biased_emax(m);
+  if (e == 0) return;  // all-zero block: the staged words stay zero
+  st.or_word(0, (2u * e + 1u) & 0x1ffu);
+  int v[64];
+  {
+    const float s = quant_scale(e);
+#pragma unroll
+    for (int i = 0; i < 64; i++) v[i] = f2i_rz(s * f[i]);
+  }
+  fwd_xform3_bal(v, kc);
+  uint32_t u[64];
+  fwd_order<3>(v, u, std::make_integer_sequence<int, 64>{});
+
+  SigState sg;
+  sg.set(0);
+  int off = 9;
+  for (int c = 3; c >= 0; c--) {  // planes 8c+7 .. 8c
+    const uint32_t sel = (uint32_t)c | ((uint32_t)(4 + c) << 4);
+    uint32_t lo[8], hi[8];
+    planes_of_byte_bal<0>(u, sel, lo, kc);
+    planes_of_byte_bal<1>(u, sel, hi, kc);
+    int count = 0;
+#pragma unroll
+    for (int k = 7; k >= 0; k--) {
+      const bool live = off < maxbits;
+      if (warp_all(!live || sg.n >= 64)) {
+        // every lane of the warp copies the plane verbatim (or is finished)
+        if (live) {
+          stage_put64(st, off, lo[k], hi[k]);
+          off += 64;
+        }
+      } else if (live) {
+        // n < 64 on some lane: one predicated path for all of them.  With
+        // n == 64 the masks select the whole word and nothing is left over.
+        const int n = sg.n, s = n & 31;
+        const uint32_t fl = funnel_r(lo[k], hi[k], s), sh = hi[k] >> s;
+        const uint32_t xl = n >= 64 ? 0u : (n < 32 ? fl : sh);
+        const uint32_t xh = n < 32 ? sh : 0u;
+        const bool any = (xl | xh) != 0u;
+        stage_put64(st, off, (lo[k] & sg.mlo) | (any ? sg.glo : 0u), (hi[k] & sg.mhi) | (any ? sg.ghi : 0u));
+        off += n < 64 ? n + 1 : 64;
+        if (any) {
+          const int top = (int)(hi[k] >> 31);
+          const int msb = hi[k] ? 64 - clz32(hi[k]) : 32 - clz32(lo[k]);
+          if (off < maxbits) {
+            st.q_put(count, 0, xl);
+            st.q_put(count, 1, xh);
+            st.q_put(count, 2, (uint32_t)off | ((uint32_t)top << 31));
+            count++;
+          }
+          off += (msb - n) + popc32(xl) + popc32(xh) - 2 * top;
+          sg.set(msb);
+        }
+      }
+    }
+    // work off this lane's expansions
+    int slot = 0;
+    bool have = count > 0;
+    uint32_t xl = 0, xh = 0;
+    int boff = 0, top = 0;
+    if (have) {
+      xl = st.q_get(0, 0);
+      xh = st.q_get(0, 1);
+      const uint32_t meta = st.q_get(0, 2);
+      boff = (int)(meta & 0x7fffffffu);
+      top = (int)(meta >> 31);
+    }
+    while (have) {
+      const uint32_t en = enc_lut[xl & 0xffu];
+      xl = funnel_r(xl, xh, 8);
+      xh >>= 8;
+      const bool more = (xl | xh) != 0u;
+      const int lf = (int)(en >> 24);
+      const int len = more ? (int)((en >> 16) & 0x1fu) : lf - 2 * top;
+      const uint32_t keep = more ? 0xffffu : low_mask32(lf - 1 - top);
+      const uint32_t pat = en & keep;
+      const int s = boff & 31, w = boff >> 5;
+      st.or_word(w, pat << s);
+      st.or_word(w + 1, funnel_l(pat, 0u, s));
+      boff += len;
+      if (!more || boff >= maxbits) {
+        slot++;
+        have = slot < count;
+        if (have) {
+          xl = st.q_get(slot, 0);
+          xh = st.q_get(slot, 1);
+          const uint32_t meta = st.q_get(slot, 2);
+          boff = (int)(meta & 0x7fffffffu);
+          top = (int)(meta >> 31);
+        }
+      }
+    }
+    if (off >= maxbits) break;
+  }
 }
 
 // ---- bit reader -------------------------------------------------------------------

@@ -94,6 +94,20 @@ struct StageSource {
   __device__ __forceinline__ uint32_t get(int w) const { return w < nwords ? p[w * kThreads] : 0u; }
 };
 
+// Staged words and the per-lane expansion queue of the staged encoder, both
+// word-major so that a warp's lanes always hit 32 different banks.
+struct SmemStage {
+  uint32_t* p;  // &stage[threadIdx.x]
+  uint32_t* q;  // &queue[threadIdx.x]
+  __device__ __forceinline__ void or_word(int w, uint32_t v) { atomicOr(p + w * kThreads, v); }
+  __device__ __forceinline__ void q_put(int slot, int field, uint32_t v) {
+    q[(slot * QUEUE_FIELDS + field) * kThreads] = v;
+  }
+  __device__ __forceinline__ uint32_t q_get(int slot, int field) const {
+    return q[(slot * QUEUE_FIELDS + field) * kThreads];
+  }
+};
+
 // z-slab that feeds row z of a block with vz valid slabs (encode.cuh:17-38
 // applied along z: a,a,a,a / a,b,b,a / a,b,c,a)
 __device__ __forceinline__ int pad_src_z(int z, int vz) { return z < vz ? z : (z == 3 ? 0 : vz - 1); }
@@ -105,16 +119,18 @@ __device__ __forceinline__ int pad_src_z(int z, int vz) { return z < vz ? z : (z
 // =====================================================================================
 __global__ void __launch_bounds__(kThreads, 2)
 zfp_encode_slab_kernel(const float* __restrict__ in, uint32_t* __restrict__ out, uint32_t nz, int maxbits,
-                       int* __restrict__ status) {
+                       int* __restrict__ status, const PipeConsts kc) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   float* tile = reinterpret_cast<float*>(smem_raw);
   uint32_t* stage = reinterpret_cast<uint32_t*>(smem_raw + kGroupBytes);
   const int nwords = maxbits >> 5;
-  uint32_t* lut = stage + nwords * kThreads;
+  uint32_t* queue = stage + (nwords + STAGE_SPARE_ROWS) * kThreads;
+  uint32_t* lut = queue + QUEUE_SLOTS * QUEUE_FIELDS * kThreads;
   __shared__ __align__(8) uint64_t bar;
 
   const int tid = threadIdx.x;
   lut[tid] = enc_lut_entry((uint32_t)tid);
+  for (int w = 0; w < nwords; w++) stage[w * kThreads + tid] = 0u;  // coded bits are OR-ed in
   if (tid == 0) {
     mbar_init(&bar, 1);
     fence_async_smem();
@@ -166,8 +182,8 @@ zfp_encode_slab_kernel(const float* __restrict__ in, uint32_t* __restrict__ out,
     if (tid == 0 && g + gridDim.x < ngroups) issue(g + gridDim.x);
 
     if (vz > 0) {
-      StageSink sink{stage + tid};
-      encode_block<3>(f, maxbits, sink, lut);
+      SmemStage st{stage + tid, queue + tid};
+      encode_block3_staged(f, maxbits, st, lut, kc);
     }
     __syncthreads();
 
@@ -179,12 +195,16 @@ zfp_encode_slab_kernel(const float* __restrict__ in, uint32_t* __restrict__ out,
       const uint32_t per = nwords >> 2, chunks = nblk * per;
       for (uint32_t q = tid; q < chunks; q += kThreads) {
         const uint32_t b = q / per, c = q - b * per;
-        const uint32_t* s = stage + (4 * c) * kThreads + b;
+        uint32_t* s = stage + (4 * c) * kThreads + b;
         uint4 v;
         v.x = s[0];
         v.y = s[kThreads];
         v.z = s[2 * kThreads];
         v.w = s[3 * kThreads];
+        s[0] = 0u;  // ready for the next group
+        s[kThreads] = 0u;
+        s[2 * kThreads] = 0u;
+        s[3 * kThreads] = 0u;
         reinterpret_cast<uint4*>(dst)[q] = v;
       }
     } else {
@@ -192,6 +212,7 @@ zfp_encode_slab_kernel(const float* __restrict__ in, uint32_t* __restrict__ out,
       for (uint32_t q = tid; q < words; q += kThreads) {
         const uint32_t b = q / nwords, w = q - b * nwords;
         dst[q] = stage[w * kThreads + b];
+        stage[w * kThreads + b] = 0u;
       }
     }
     // the next iteration writes `stage` only after its own first barrier
@@ -346,7 +367,9 @@ zfp_decode_generic_kernel(FieldGeom g, const uint32_t* __restrict__ in, float* _
 // launchers
 // =====================================================================================
 static size_t slab_smem_bytes(int maxbits, bool decode) {
-  return (size_t)kGroupBytes + (size_t)(maxbits >> 5) * kThreads * 4 + (decode ? DEC_LUT_SIZE : ENC_LUT_SIZE) * 4;
+  if (decode) return (size_t)kGroupBytes + (size_t)(maxbits >> 5) * kThreads * 4 + DEC_LUT_SIZE * 4;
+  return (size_t)kGroupBytes + (size_t)((maxbits >> 5) + STAGE_SPARE_ROWS + QUEUE_SLOTS * QUEUE_FIELDS) * kThreads * 4 +
+         ENC_LUT_SIZE * 4;
 }
 
 bool zfp_slab_eligible(const FieldGeom& g, const void* field, const void* stream, int maxbits) {
@@ -370,7 +393,7 @@ cudaError_t zfp_encode_launch(const FieldGeom& g, const float* in, void* out, in
                                          (int)slab_smem_bytes(2048, false));
     if (e != cudaSuccess) return e;
     zfp_encode_slab_kernel<<<slab_grid(g.nz, 2 * sm_count), kThreads, smem, stream>>>(
-        in, reinterpret_cast<uint32_t*>(out), g.nz, maxbits, d_status);
+        in, reinterpret_cast<uint32_t*>(out), g.nz, maxbits, d_status, pipe_consts());
     return cudaGetLastError();
   }
   if (maxbits & 31) {

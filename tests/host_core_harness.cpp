@@ -6,6 +6,7 @@
 #include <cmath>
 #include <cstdint>
 #include <cstring>
+#include <algorithm>
 #include <vector>
 
 #include "../cswap_b200/csrc/zfp_field.cuh"
@@ -57,7 +58,32 @@ void decode_field(const csw::FieldGeom& g, const uint32_t* in, int maxbits, floa
 }
 }  // namespace
 
+struct HostStage {
+  uint32_t* w;
+  uint32_t q[csw::QUEUE_SLOTS][csw::QUEUE_FIELDS];
+  void or_word(int i, uint32_t v) { w[i] |= v; }
+  void q_put(int s, int f, uint32_t v) { q[s][f] = v; }
+  uint32_t q_get(int s, int f) const { return q[s][f]; }
+};
+
 extern "C" {
+// the staged 3-D encoder of the slab kernel (nx, ny, nz arbitrary here; whole words per block)
+void core_encode_staged(const float* in, size_t nx, size_t ny, size_t nz, int maxbits, uint32_t* out) {
+  csw::FieldGeom g = csw::make_geom(nx, ny, nz, 0, 0, 0);
+  auto lut = enc_lut();
+  const csw::PipeConsts kc = csw::pipe_consts();
+  const int nw = maxbits / 32;
+  std::vector<uint32_t> rows(nw + csw::STAGE_SPARE_ROWS);
+  size_t nb = csw::geom_blocks(g);
+  for (size_t b = 0; b < nb; b++) {
+    float q[64];
+    csw::gather_block<3>(g, in, b, q);
+    std::fill(rows.begin(), rows.end(), 0u);
+    HostStage st{rows.data(), {}};
+    csw::encode_block3_staged(q, maxbits, st, lut.data(), kc);
+    for (int i = 0; i < nw; i++) out[b * nw + i] = rows[i];
+  }
+}
 // maxbits must be a multiple of 32 here (whole words per block)
 void core_encode(const float* in, size_t nx, size_t ny, size_t nz, int maxbits, uint32_t* out) {
   csw::FieldGeom g = csw::make_geom(nx, ny, nz, 0, 0, 0);
