@@ -108,6 +108,8 @@ struct SmemStage {
   }
 };
 
+__host__ __device__ constexpr bool encode_queue_in_tile(int maxbits) { return maxbits > 768; }
+
 // z-slab that feeds row z of a block with vz valid slabs (encode.cuh:17-38
 // applied along z: a,a,a,a / a,b,b,a / a,b,c,a)
 __device__ __forceinline__ int pad_src_z(int z, int vz) { return z < vz ? z : (z == 3 ? 0 : vz - 1); }
@@ -124,8 +126,13 @@ zfp_encode_slab_kernel(const float* __restrict__ in, uint32_t* __restrict__ out,
   float* tile = reinterpret_cast<float*>(smem_raw);
   uint32_t* stage = reinterpret_cast<uint32_t*>(smem_raw + kGroupBytes);
   const int nwords = maxbits >> 5;
-  uint32_t* queue = stage + (nwords + STAGE_SPARE_ROWS) * kThreads;
-  uint32_t* lut = queue + QUEUE_SLOTS * QUEUE_FIELDS * kThreads;
+  // At high rates the staged words leave no room for a separate expansion queue
+  // if two CTAs are to share an SM: the queue then lives in the tile buffer and
+  // the next group's copy is issued only after coding (the other CTA covers it).
+  const bool queue_in_tile = encode_queue_in_tile(maxbits);
+  uint32_t* after_stage = stage + (nwords + STAGE_SPARE_ROWS) * kThreads;
+  uint32_t* queue = queue_in_tile ? reinterpret_cast<uint32_t*>(tile) : after_stage;
+  uint32_t* lut = queue_in_tile ? after_stage : after_stage + QUEUE_SLOTS * QUEUE_FIELDS * kThreads;
   __shared__ __align__(8) uint64_t bar;
 
   const int tid = threadIdx.x;
@@ -179,13 +186,14 @@ zfp_encode_slab_kernel(const float* __restrict__ in, uint32_t* __restrict__ out,
       }
     }
     __syncthreads();  // every lane holds its block: the tile may be overwritten
-    if (tid == 0 && g + gridDim.x < ngroups) issue(g + gridDim.x);
+    if (!queue_in_tile && tid == 0 && g + gridDim.x < ngroups) issue(g + gridDim.x);
 
     if (vz > 0) {
       SmemStage st{stage + tid, queue + tid};
       encode_block3_staged(f, maxbits, st, lut, kc);
     }
     __syncthreads();
+    if (queue_in_tile && tid == 0 && g + gridDim.x < ngroups) issue(g + gridDim.x);
 
     // coalesced write-out of the group's blocks (block-major, nwords each)
     const uint32_t tiles = ((nz + 3) >> 2) - g * 4 < 4 ? ((nz + 3) >> 2) - g * 4 : 4;
@@ -368,7 +376,8 @@ zfp_decode_generic_kernel(FieldGeom g, const uint32_t* __restrict__ in, float* _
 // =====================================================================================
 static size_t slab_smem_bytes(int maxbits, bool decode) {
   if (decode) return (size_t)kGroupBytes + (size_t)(maxbits >> 5) * kThreads * 4 + DEC_LUT_SIZE * 4;
-  return (size_t)kGroupBytes + (size_t)((maxbits >> 5) + STAGE_SPARE_ROWS + QUEUE_SLOTS * QUEUE_FIELDS) * kThreads * 4 +
+  const int queue_rows = encode_queue_in_tile(maxbits) ? 0 : QUEUE_SLOTS * QUEUE_FIELDS;
+  return (size_t)kGroupBytes + (size_t)((maxbits >> 5) + STAGE_SPARE_ROWS + queue_rows) * kThreads * 4 +
          ENC_LUT_SIZE * 4;
 }
 
