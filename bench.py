@@ -44,6 +44,9 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--mib", type=int, default=256, help="tensor size in MiB (float32)")
     ap.add_argument("--rate", type=int, default=8, help="ZFP bits per value")
+    ap.add_argument("--workload", default="zfp", choices=["zfp", "vgg16", "bert"],
+                    help="zfp: codec round trip (headline); vgg16 / bert: one swapped training step")
+    ap.add_argument("--batch", type=int, default=0, help="batch size of the model workloads (0: 128 / 32)")
     ap.add_argument("--no-extra", action="store_true", help="skip the sparse / swap-link side measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     return ap.parse_args()
@@ -204,10 +207,115 @@ def workload_config(args):
             "parallelism": f"{args.gpus} independent replica(s), no collective"}
 
 
+def run_model_workload(args):
+    """Swapped training step (VGG16 batch 128 on 3x32x32, or BERT-base-shaped
+    encoder batch 32 x seq 512): step latency without swapping, with raw swap of
+    every activation (vDNN-style), with the reference's hard-wired split and
+    with the cost model's per-tensor choice, plus the bytes each puts on the
+    host link."""
+    import torch
+    import torch.distributed as dist
+    import cswap_b200 as cs
+    from cswap_b200 import workloads as W
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    torch.manual_seed(1 + rank)
+    if args.workload == "vgg16":
+        batch = args.batch or 128
+        model = W.VGG16().to(dev).train()
+        hx = torch.randn(batch, 3, 32, 32).pin_memory()
+        hy = torch.randint(0, 10, (batch,)).pin_memory()
+        maxbits, pinned, staging, nids = 512, 2 << 30, 512 << 20, 64
+        name = f"VGG16 CIFAR-10-shaped training step, fp32, batch {batch}, synthetic 3x32x32 inputs"
+    else:
+        batch = args.batch or 32
+        model = W.BertEncoder().to(dev).train()
+        hx = torch.randint(0, 30522, (batch, 512)).pin_memory()
+        hy = torch.randint(0, 2, (batch,)).pin_memory()
+        maxbits, pinned, staging, nids = 1024, 24 << 30, 4 << 30, 400
+        name = f"BERT-base-shaped encoder training step, fp32, batch {batch}, seq 512, 12 layers"
+    mgr = cs.SwapManager(pinned_bytes=pinned, staging_bytes=staging, zfp_maxbits=maxbits)
+    make_batch = lambda: (hx, hy)
+    steps, warmup = max(1, min(args.steps, 20)), max(3, min(args.warmup, 5))
+
+    def fresh(policy_fn):
+        exe = cs.Execution(mgr=mgr)
+        exe.init_(nids)
+        policy_fn(exe)
+        return exe
+
+    def all_raw(exe):
+        for i in range(nids):
+            exe.begin_stage[i] = i + 1
+            exe.policy[i] = cs.POLICY_RAW
+
+    results = {}
+    results["no_swap"] = W.timed_steps(model, fresh(lambda e: None), make_batch, steps, warmup)
+    results["raw_swap"] = W.timed_steps(model, fresh(all_raw), make_batch, steps, warmup)
+    if args.workload == "vgg16":
+        results["reference_split_zfp8"] = W.timed_steps(model, fresh(W.vgg16_reference_policy), make_batch, steps,
+                                                        warmup)
+    # self-tuning: profile one step, fit the cost model on this GPU, decide per tensor
+    exe = fresh(lambda e: None)
+    exe.profile = True
+    x, y = hx.to(dev), hy.to(dev)
+    if x.is_floating_point():
+        x.requires_grad_(True)
+    model.forward_with(exe, x, y).backward()
+    prof = exe.finish_profile()
+    cm = cs.CostModel.fit(mgr, maxbits)
+    lossy = None if args.workload == "vgg16" else [i for i, p in prof.items() if p["float32"]]
+    policy = exe.make_policy(prof, cm, lossy_ids=lossy)
+    results["self_tuned"] = W.timed_steps(model, exe, make_batch, steps, warmup)
+    counts = {str(k): policy.count(k) for k in (0, 2, 3, 6)}
+    # the same decision when loss is acceptable on every float activation
+    exe_all = fresh(lambda e: None)
+    policy_all = exe_all.make_policy(prof, cm, lossy_ids=[i for i, p in prof.items() if p["float32"]])
+    results["self_tuned_lossy_everywhere"] = W.timed_steps(model, exe_all, make_batch, steps, warmup)
+    counts_all = {str(k): policy_all.count(k) for k in (0, 2, 3, 6)}
+    t_tuned, t_raw, t_none = (max_over_ranks([results[k]["ms_per_step"]], dev)[0]
+                              for k in ("self_tuned", "raw_swap", "no_swap"))
+    raw, tuned = results["raw_swap"], results["self_tuned"]
+    if rank == 0:
+        line = {
+            "metric": f"{args.workload}_swapped_step_ms", "value": t_tuned, "unit": "ms/step", "n_gpus": world,
+            "steps": steps, "warmup": warmup, "ms_per_step": t_tuned, "higher_is_better": False, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": name, "parallelism": f"{world} independent replica(s), no collective",
+                       "zfp_maxbits": maxbits, "policy_counts": counts,
+                       "policy_counts_lossy_everywhere": counts_all},
+            "step_ms": {"no_swap": t_none, "raw_swap": t_raw, "self_tuned": t_tuned,
+                        "self_tuned_lossy_everywhere": results["self_tuned_lossy_everywhere"]["ms_per_step"],
+                        **({"reference_split_zfp8": results["reference_split_zfp8"]["ms_per_step"]}
+                           if "reference_split_zfp8" in results else {})},
+            "raw_swap": raw, "self_tuned": tuned,
+            "activation_bytes_per_link_byte": {
+                "raw_swap": raw["activation_bytes_per_step"] / max(raw["link_bytes_out_per_step"], 1),
+                "self_tuned": tuned["activation_bytes_per_step"] / max(tuned["link_bytes_out_per_step"], 1),
+                "self_tuned_lossy_everywhere":
+                    results["self_tuned_lossy_everywhere"]["activation_bytes_per_step"] /
+                    max(results["self_tuned_lossy_everywhere"]["link_bytes_out_per_step"], 1)},
+            "cost_model": cm.as_dict(),
+        }
+        print(json.dumps(line))
+    mgr.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.workload != "zfp":
+        run_model_workload(args)
         return
 
     import torch

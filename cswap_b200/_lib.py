@@ -48,7 +48,7 @@ class CostModelStruct(C.Structure):
 
 class TensorDescStruct(C.Structure):
     _fields_ = [("numel", C.c_size_t), ("zero_fraction", C.c_double), ("lossy_ok", C.c_int),
-                ("overlap_fwd_s", C.c_double), ("overlap_bwd_s", C.c_double)]
+                ("ready_s", C.c_double), ("need_s", C.c_double)]
 
 
 class Bitstream(C.Structure):
@@ -102,6 +102,7 @@ SIGNATURES = {
     "csw_mgr_get_streams": (_I, [_P, C.POINTER(_P), C.POINTER(_P), C.POINTER(_P)]),
     "csw_swap_out": (_I, [_P, _P, _SZ, _I, _P, C.POINTER(_P)]),
     "csw_swap_out_done": (_I, [_P, _P, C.POINTER(_I)]),
+    "csw_swap_out_sync": (_I, [_P, _P]),
     "csw_swap_out_wait": (_I, [_P, _P, _P]),
     "csw_prefetch": (_I, [_P, _P]),
     "csw_swap_in": (_I, [_P, _P, _P, _P]),
@@ -111,7 +112,7 @@ SIGNATURES = {
     "csw_mgr_reset_stats": (_I, [_P]),
     "csw_mgr_sync": (_I, [_P]),
     "csw_cost_fit": (_I, [_P, C.POINTER(CostModelStruct)]),
-    "csw_cost_decide": (_I, [C.POINTER(CostModelStruct), C.POINTER(TensorDescStruct), _SZ, C.POINTER(_I),
+    "csw_cost_decide": (_I, [C.POINTER(CostModelStruct), C.POINTER(TensorDescStruct), _SZ, C.c_double, C.POINTER(_I),
                              C.POINTER(C.c_double)]),
     "csw_host_alloc": (_I, [_SZ, C.POINTER(_P)]),
     "csw_host_free": (_I, [_P]),

@@ -166,48 +166,105 @@ csw_status csw_cost_fit(csw_mgr* m, csw_cost_model* model) {
   return st;
 }
 
-// Forward and backward are each simulated as one serial link shared by the
-// tensors in order.  A swap-out may start when its tensor's consumer has run
-// (time 0 of its window) and is "exposed" by however long it outlasts the
-// window overlap_fwd; a swap-in may start overlap_bwd before it is needed.
-// Link occupancy carries over from tensor to tensor, so compressing an early
-// tensor helps the later ones.  Lossless choices win ties; ZFP is chosen only
-// when it lowers the exposed time by more than 2 %.
-csw_status csw_cost_decide(const csw_cost_model* cm, const csw_tensor_desc* td, size_t n, int* policy,
-                           double* exposed) {
+namespace {
+
+struct Cand {
+  int policy;
+  double enc, dec, moved;
+  bool ok;
+};
+
+// One step under a given choice per tensor.  Swap-outs queue on the D2H link
+// in forward order, each no earlier than its tensor is ready plus its encode
+// time; forward compute never waits for them.  Backward needs the tensors in
+// reverse order; the H2D copy of a tensor starts when the tensor swapped out
+// after it was asked for (one step of prefetch), not before its own D2H has
+// finished and not before the link is free; if copy + decode end after the
+// tensor is needed, backward stalls and everything later shifts.  Returns the
+// total stall and writes the per-tensor stalls.
+double simulate(const csw_cost_model* cm, const csw_tensor_desc* td, size_t n, const std::vector<Cand>& c,
+                double fwd_total, double* stalls) {
+  std::vector<double> on_host(n);
+  double link = 0;
+  for (size_t i = 0; i < n; i++) {
+    if (c[i].policy == CSW_POLICY_KEEP) { on_host[i] = 0; continue; }
+    const double start = std::max(td[i].ready_s + c[i].enc, link);
+    link = start + cm->d2h_a + c[i].moved / cm->d2h_bps;
+    on_host[i] = link;
+  }
+  double stall = 0, h2d = fwd_total, asked = fwd_total;
+  for (size_t j = n; j-- > 0;) {
+    if (stalls) stalls[j] = 0;
+    if (c[j].policy == CSW_POLICY_KEEP) continue;
+    const double need = fwd_total + td[j].need_s + stall;
+    const double start = std::max(std::max(h2d, on_host[j]), asked);
+    h2d = start + cm->h2d_a + c[j].moved / cm->h2d_bps;
+    const double arrive = h2d + c[j].dec;
+    if (arrive > need) {
+      stall += arrive - need;
+      if (stalls) stalls[j] = arrive - need;
+    }
+    asked = std::max(need, arrive);
+  }
+  return stall;
+}
+
+}  // namespace
+
+// Starts from raw swap everywhere and switches tensors, largest first, to the
+// sparse codec (lossless, needs a measured zero fraction) or to ZFP (only where
+// loss is allowed) whenever the simulated stall of the whole step drops -
+// by anything for the lossless codec; ZFP must beat the best lossless choice by
+// 2 % of the tensor's raw link time (and 5 us).
+// When the links keep up with compute nothing stalls and everything stays raw.
+csw_status csw_cost_decide(const csw_cost_model* cm, const csw_tensor_desc* td, size_t n, double fwd_total_s,
+                           int* policy, double* exposed) {
   if (!cm || (!td && n) || (!policy && n)) return CSW_ERR_ARG;
   if (cm->d2h_bps <= 0 || cm->h2d_bps <= 0) return CSW_ERR_ARG;
   const double rate = cm->zfp_maxbits ? cm->zfp_maxbits / 64.0 : 8.0;  // bits per value
-  double out_busy = 0, in_busy = 0;  // backlog (seconds) the links carry into the next tensor
+  std::vector<Cand> raw(n), sparse(n), zfp(n), cur(n);
+  std::vector<size_t> order(n);
   for (size_t i = 0; i < n; i++) {
-    const double raw = (double)td[i].numel * 4.0;
-    struct Cand { int policy; double enc, dec, moved; bool ok; } c[3];
-    c[0] = {CSW_POLICY_RAW, 0, 0, raw, true};
-    const double zf = td[i].zero_fraction;
-    c[1] = {CSW_POLICY_SPARSE, cm->sparse_enc_a + cm->sparse_enc_b * raw, cm->sparse_dec_a + cm->sparse_dec_b * raw,
-            raw * (1.0 - (zf < 0 ? 0 : zf)) + raw / 32.0 + (double)td[i].numel / 1024.0, zf >= 0};
-    c[2] = {CSW_POLICY_ZFP, cm->zfp_enc_a + cm->zfp_enc_b * raw, cm->zfp_dec_a + cm->zfp_dec_b * raw,
-            raw * rate / 32.0, td[i].lossy_ok && td[i].numel % 1024 == 0 && td[i].numel > 0};
-    int best = 0;
-    double best_cost = 0, best_out = 0, best_in = 0;
-    for (int k = 0; k < 3; k++) {
-      if (!c[k].ok) continue;
-      const double t_out = out_busy + c[k].enc + cm->d2h_a + c[k].moved / cm->d2h_bps;
-      const double t_in = in_busy + cm->h2d_a + c[k].moved / cm->h2d_bps + c[k].dec;
-      const double ex = std::max(0.0, t_out - td[i].overlap_fwd_s) + std::max(0.0, t_in - td[i].overlap_bwd_s);
-      const double need = k == 2 ? 0.98 : 1.0;  // lossy must clearly pay
-      if (k == 0 || ex < best_cost * need - 1e-12) {
-        best = k;
-        best_cost = ex;
-        best_out = std::max(0.0, t_out - td[i].overlap_fwd_s);
-        best_in = std::max(0.0, t_in - td[i].overlap_bwd_s);
+    const double b = (double)td[i].numel * 4.0, zf = td[i].zero_fraction;
+    raw[i] = {CSW_POLICY_RAW, 0, 0, b, true};
+    sparse[i] = {CSW_POLICY_SPARSE, cm->sparse_enc_a + cm->sparse_enc_b * b, cm->sparse_dec_a + cm->sparse_dec_b * b,
+                 b * (1.0 - (zf < 0 ? 0 : zf)) + b / 32.0 + (double)td[i].numel / 1024.0, zf >= 0};
+    zfp[i] = {CSW_POLICY_ZFP, cm->zfp_enc_a + cm->zfp_enc_b * b, cm->zfp_dec_a + cm->zfp_dec_b * b, b * rate / 32.0,
+              td[i].lossy_ok && td[i].numel % 1024 == 0 && td[i].numel > 0};
+    cur[i] = raw[i];
+    order[i] = i;
+  }
+  std::sort(order.begin(), order.end(), [&](size_t a, size_t b2) { return td[a].numel > td[b2].numel; });
+  double best = simulate(cm, td, n, cur, fwd_total_s, nullptr);
+  for (int pass = 0; pass < 3 && best > 0; pass++) {
+    bool changed = false;
+    for (size_t oi = 0; oi < n && best > 0; oi++) {
+      const size_t i = order[oi];
+      const Cand keep = cur[i];
+      Cand pick = keep;
+      double pick_stall = best;
+      if (sparse[i].ok && keep.policy != CSW_POLICY_SPARSE) {
+        cur[i] = sparse[i];
+        const double st = simulate(cm, td, n, cur, fwd_total_s, nullptr);
+        if (st < pick_stall - 1e-7) { pick = sparse[i]; pick_stall = st; }
       }
+      if (zfp[i].ok && keep.policy != CSW_POLICY_ZFP) {
+        cur[i] = zfp[i];
+        const double st = simulate(cm, td, n, cur, fwd_total_s, nullptr);
+        // lossy has to buy a real gain: at least 2 % of the tensor's own raw link time (and 5 us)
+        const double margin = std::max(5e-6, 0.02 * raw[i].moved / cm->d2h_bps);
+        if (st < pick_stall - margin) { pick = zfp[i]; pick_stall = st; }
+      }
+      cur[i] = pick;
+      if (pick.policy != keep.policy) { changed = true; best = pick_stall; }
     }
-    policy[i] = c[best].policy;
-    if (exposed) exposed[i] = best_cost;
-    // whatever did not fit in this tensor's window delays the next one
-    out_busy = best_out;
-    in_busy = best_in;
+    if (!changed) break;
+  }
+  std::vector<double> stalls(n);
+  simulate(cm, td, n, cur, fwd_total_s, stalls.data());
+  for (size_t i = 0; i < n; i++) {
+    policy[i] = cur[i].policy;
+    if (exposed) exposed[i] = stalls[i];
   }
   return CSW_OK;
 }

@@ -146,6 +146,7 @@ struct csw_mgr {
   std::vector<int> free_slots;
   std::vector<cudaEvent_t> free_events;
   std::vector<csw_ticket*> live;      // tickets whose staging may be reclaimable
+  std::vector<csw_ticket*> zombies;   // released tickets whose copies are still in flight
   csw_mgr_stats stats{};
   std::mutex mu;
 };
@@ -200,8 +201,29 @@ void finalize_moved(csw_mgr* m, csw_ticket* t) {
   m->stats.moved_bytes_out += t->moved;
 }
 
+bool event_done(cudaEvent_t ev) { return !ev || cudaEventQuery(ev) == cudaSuccess; }
+
+// Return everything a released ticket holds to the pools and free it.
+void destroy_ticket(csw_mgr* m, csw_ticket* t) {
+  free_stage(m, t);
+  if (t->host) m->pinned.release(t->host, t->host_cap);
+  if (t->nnz_slot >= 0) m->free_slots.push_back(t->nnz_slot);
+  put_event(m, t->ev_read);
+  put_event(m, t->ev_d2h);
+  put_event(m, t->ev_h2d);
+  put_event(m, t->ev_done);
+  delete t;
+}
+
 // Non-blocking housekeeping: release staging whose last user has finished.
 void poll(csw_mgr* m) {
+  size_t z = 0;
+  for (size_t i = 0; i < m->zombies.size(); i++) {
+    csw_ticket* t = m->zombies[i];
+    if (event_done(t->ev_d2h) && event_done(t->ev_h2d) && event_done(t->ev_done)) destroy_ticket(m, t);
+    else m->zombies[z++] = t;
+  }
+  m->zombies.resize(z);
   size_t k = 0;
   for (size_t i = 0; i < m->live.size(); i++) {
     csw_ticket* t = m->live[i];
@@ -232,14 +254,15 @@ void* pool_alloc(csw_mgr* m, Pool& pool, size_t bytes, size_t* got) {
   if (p) return p;
   poll(m);
   p = pool.alloc(bytes, got);
-  while (!p && !m->live.empty()) {
-    csw_ticket* t = m->live.front();
-    cudaEvent_t ev = t->state == T_OUT ? t->ev_d2h : t->ev_done;
+  while (!p && (!m->live.empty() || !m->zombies.empty())) {
+    csw_ticket* t = !m->zombies.empty() ? m->zombies.front() : m->live.front();
+    cudaEvent_t ev = t->state == T_OUT ? t->ev_d2h : (t->ev_done ? t->ev_done : t->ev_d2h);
     if (ev) cudaEventSynchronize(ev);
-    const size_t before = m->live.size();
+    if (t->state == T_DEAD && t->ev_h2d) cudaEventSynchronize(t->ev_h2d);
+    const size_t before = m->live.size() + m->zombies.size();
     poll(m);
     p = pool.alloc(bytes, got);
-    if (!p && m->live.size() == before) break;
+    if (!p && m->live.size() + m->zombies.size() == before) break;
   }
   return p;
 }
@@ -294,6 +317,8 @@ csw_status csw_mgr_destroy(csw_mgr* m) {
   if (m->s_codec) cudaStreamSynchronize(m->s_codec);
   if (m->s_d2h) cudaStreamSynchronize(m->s_d2h);
   if (m->s_h2d) cudaStreamSynchronize(m->s_h2d);
+  for (csw_ticket* t : m->zombies) destroy_ticket(m, t);
+  m->zombies.clear();
   for (cudaEvent_t ev : m->free_events) cudaEventDestroy(ev);
   if (m->s_codec) cudaStreamDestroy(m->s_codec);
   if (m->s_d2h) cudaStreamDestroy(m->s_d2h);
@@ -435,6 +460,19 @@ csw_status csw_swap_out_done(csw_mgr* m, csw_ticket* t, int* done) {
   return CSW_OK;
 }
 
+csw_status csw_swap_out_sync(csw_mgr* m, csw_ticket* t) {
+  if (!m || !t) return CSW_ERR_ARG;
+  cudaEvent_t ev;
+  {
+    std::lock_guard<std::mutex> lk(m->mu);
+    if (t->state == T_DEAD) return CSW_ERR_STATE;
+    ev = t->ev_read;
+  }
+  DeviceGuard g(m->device);
+  cudaError_t e = cudaEventSynchronize(ev);
+  return e == cudaSuccess ? CSW_OK : cuda_fail(e);
+}
+
 csw_status csw_swap_out_wait(csw_mgr* m, csw_ticket* t, csw_stream_t stream) {
   if (!m || !t) return CSW_ERR_ARG;
   std::lock_guard<std::mutex> lk(m->mu);
@@ -550,23 +588,15 @@ csw_status csw_ticket_release(csw_mgr* m, csw_ticket* t) {
   std::lock_guard<std::mutex> lk(m->mu);
   DeviceGuard g(m->device);
   if (t->state == T_DEAD) return CSW_ERR_STATE;
-  // memory may only go back to the pools once nothing in flight touches it
-  cudaError_t e = cudaSuccess;
-  if (t->ev_d2h) e = cudaEventSynchronize(t->ev_d2h);
-  if (e == cudaSuccess && t->ev_h2d) e = cudaEventSynchronize(t->ev_h2d);
-  if (e == cudaSuccess && t->ev_done) e = cudaEventSynchronize(t->ev_done);
-  if (e != cudaSuccess) return cuda_fail(e);
-  if (t->policy == CSW_POLICY_SPARSE && !t->moved_final) finalize_moved(m, t);
+  // Never blocks: memory goes back to the pools now if nothing in flight
+  // touches it, otherwise as soon as a later call finds its copies finished.
+  const bool idle = event_done(t->ev_d2h) && event_done(t->ev_h2d) && event_done(t->ev_done);
+  cudaGetLastError();
+  if (idle && t->policy == CSW_POLICY_SPARSE && !t->moved_final) finalize_moved(m, t);
   t->state = T_DEAD;
   poll(m);  // drops it from the live list
-  free_stage(m, t);
-  if (t->host) m->pinned.release(t->host, t->host_cap);
-  if (t->nnz_slot >= 0) m->free_slots.push_back(t->nnz_slot);
-  put_event(m, t->ev_read);
-  put_event(m, t->ev_d2h);
-  put_event(m, t->ev_h2d);
-  put_event(m, t->ev_done);
-  delete t;
+  if (idle) destroy_ticket(m, t);
+  else m->zombies.push_back(t);
   return CSW_OK;
 }
 

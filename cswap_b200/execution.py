@@ -31,6 +31,7 @@ from typing import Dict, List, Optional, Sequence, Union
 import torch
 
 from .codec import POLICY_DROP, POLICY_KEEP, POLICY_RAW, POLICY_SPARSE, POLICY_ZFP
+from ._lib import CswapError
 from .swap import CostModel, SwapManager, TensorDesc, Ticket
 
 
@@ -100,6 +101,7 @@ class Execution:
         self._prof: Dict[int, dict] = {}
         self._prof_start = None
         self.swapped_tensors = 0
+        self.skipped_for_memory = 0
 
     # ---- set-up (Execution.h:46-64) -------------------------------------------
     def init_(self, n: int, zfp_maxbits: Optional[int] = None) -> None:
@@ -182,7 +184,13 @@ class Execution:
             rec = self._record_for(t)
             if rec.ticket is not None:
                 continue
-            rec.ticket = self.mgr.swap_out(rec.tensor, pol)
+            try:
+                rec.ticket = self.mgr.swap_out(rec.tensor, pol)
+            except CswapError as err:
+                if err.status != 4:  # pools exhausted: this tensor simply stays on the device
+                    raise
+                self.skipped_for_memory += 1
+                continue
             rec.order = len(self._swapped)
             self._swapped.append(weakref.ref(rec))
             self._pending.append(rec)
@@ -227,17 +235,23 @@ class Execution:
         return out
 
     def make_policy(self, prof: Dict[int, dict], cost: CostModel, lossy_ids: Optional[Sequence[int]] = None,
-                    lookahead: int = 2, bwd_factor: float = 2.0, min_bytes: int = 1 << 20) -> List[int]:
+                    bwd_factor: float = 2.0, min_bytes: int = 1 << 20) -> List[int]:
         """Fill `policy` / `begin_stage` from a profiled iteration.
 
         Tensor id i (the output of layer i) becomes a swap candidate at the
-        first layer that consumes it.  Its swap-out may hide behind the next
-        `lookahead` layers of forward compute and its swap-in behind
-        `bwd_factor` times as much backward compute.  ZFP is allowed on the
-        ids in `lossy_ids` (default: inputs of CONV layers, which is where the
+        first layer that consumes it.  The cost model gets, per candidate, the
+        forward time at which that consumer starts and the backward compute
+        that precedes the consumer's backward (taken as `bwd_factor` times the
+        forward time of the layers after it), and simulates the step's link
+        traffic to choose raw / sparse / ZFP.  ZFP is allowed on the ids in
+        `lossy_ids` (default: inputs of CONV layers, which is where the
         reference's drivers apply it, vgg16-cifar10.cpp:381-397)."""
         n = max(prof) + 1 if prof else 0
         times = [prof[i]["time_s"] if i in prof else 0.0 for i in range(n)]
+        start = [0.0] * (n + 1)
+        for i in range(n):
+            start[i + 1] = start[i] + times[i]
+        fwd_total = start[n]
         consumer: Dict[int, int] = {}
         conv_inputs = set()
         for idx in sorted(prof):
@@ -251,15 +265,15 @@ class Execution:
             self.policy += [POLICY_KEEP] * (n - len(self.policy))
             self.begin_stage += [0] * (n - len(self.begin_stage))
         cands, descs = [], []
-        for tid in sorted(consumer):
+        for tid in sorted(consumer, key=lambda t: consumer[t]):
             p = prof.get(tid)
             if p is None or p["omit"] or not p["float32"] or not p["has_grad"] or p["numel"] * 4 < min_bytes:
                 continue
             c = consumer[tid]
-            window = sum(times[c:c + lookahead])
             cands.append(tid)
-            descs.append(TensorDesc(p["numel"], p["zero_fraction"], tid in lossy, window, bwd_factor * window))
-        pol, _ = cost.decide(descs)
+            descs.append(TensorDesc(p["numel"], p["zero_fraction"], tid in lossy, ready_s=start[c],
+                                    need_s=bwd_factor * (fwd_total - start[c + 1])))
+        pol, _ = cost.decide(descs, fwd_total)
         for tid in range(n):
             self.policy[tid] = POLICY_KEEP
         for tid, pcode in zip(cands, pol):

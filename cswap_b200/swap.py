@@ -33,11 +33,16 @@ class Ticket:
                 "complete": bool(ti.complete)}
 
     def release(self) -> None:
-        if self._h is not None and self._mgr._h is not None:
-            check(lib().csw_ticket_release(self._mgr._h, self._h), "csw_ticket_release")  # waits for its copies
+        """Give the ticket up; its pool memory returns once its copies have finished."""
+        mgr = self._mgr
+        if self._h is not None and mgr._h is not None:
+            if any(tk is self for tk, _ in mgr._reading):
+                # the source tensor is still held for the device's sake: it may
+                # only be dropped once the device has finished reading it
+                check(lib().csw_swap_out_sync(mgr._h, self._h), "csw_swap_out_sync")
+                mgr._reading = [(tk, t) for tk, t in mgr._reading if tk is not self]
+            check(lib().csw_ticket_release(mgr._h, self._h), "csw_ticket_release")
         self._h = None
-        if self._mgr is not None and self._mgr._reading:
-            self._mgr._reading = [(tk, t) for tk, t in self._mgr._reading if tk is not self]
 
     def __del__(self):
         try:
@@ -142,8 +147,8 @@ class TensorDesc:
     numel: int
     zero_fraction: float = -1.0
     lossy_ok: bool = False
-    overlap_fwd_s: float = 0.0
-    overlap_bwd_s: float = 0.0
+    ready_s: float = 0.0   # forward time at which the swap-out may start
+    need_s: float = 0.0    # backward compute that runs before the tensor is needed
 
 
 _COST_FIELDS = [n for n, _ in CostModelStruct._fields_]
@@ -168,14 +173,15 @@ class CostModel:
             check(lib().csw_cost_fit(mgr._h, C.byref(m.c)), "csw_cost_fit")
         return m
 
-    def decide(self, tensors: Sequence[TensorDesc]) -> Tuple[List[int], List[float]]:
+    def decide(self, tensors: Sequence[TensorDesc], fwd_total_s: float = 0.0) -> Tuple[List[int], List[float]]:
+        """Policy code per tensor (forward order) and its modelled stall in seconds."""
         n = len(tensors)
         arr = (TensorDescStruct * max(n, 1))()
         for i, t in enumerate(tensors):
-            arr[i] = TensorDescStruct(t.numel, t.zero_fraction, int(t.lossy_ok), t.overlap_fwd_s, t.overlap_bwd_s)
+            arr[i] = TensorDescStruct(t.numel, t.zero_fraction, int(t.lossy_ok), t.ready_s, t.need_s)
         pol = (C.c_int * max(n, 1))()
         exp = (C.c_double * max(n, 1))()
-        check(lib().csw_cost_decide(C.byref(self.c), arr, n, pol, exp), "csw_cost_decide")
+        check(lib().csw_cost_decide(C.byref(self.c), arr, n, fwd_total_s, pol, exp), "csw_cost_decide")
         return list(pol[:n]), list(exp[:n])
 
     def as_dict(self) -> dict:

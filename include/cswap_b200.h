@@ -160,6 +160,8 @@ csw_status csw_swap_out(csw_mgr* m, const float* d_ptr, size_t numel, int policy
                         csw_ticket** ticket);
 /* 1 in *done when the tensor's device bytes are no longer needed. */
 csw_status csw_swap_out_done(csw_mgr* m, csw_ticket* t, int* done);
+/* Block the host until d_ptr is no longer read. */
+csw_status csw_swap_out_sync(csw_mgr* m, csw_ticket* t);
 /* Make `stream` wait (device side) until d_ptr is no longer read. */
 csw_status csw_swap_out_wait(csw_mgr* m, csw_ticket* t, csw_stream_t stream);
 
@@ -169,7 +171,9 @@ csw_status csw_swap_out_wait(csw_mgr* m, csw_ticket* t, csw_stream_t stream);
  * wait for the result.  csw_prefetch starts the host -> device copy early. */
 csw_status csw_prefetch(csw_mgr* m, csw_ticket* t);
 csw_status csw_swap_in(csw_mgr* m, csw_ticket* t, float* d_dst, csw_stream_t compute);
-/* Return the ticket's host and staging memory to the pools. */
+/* Give the ticket up.  Never blocks: its host and staging memory return to the
+ * pools at once if no copy is in flight, else when a later call on the manager
+ * finds them finished.  The handle is invalid afterwards. */
 csw_status csw_ticket_release(csw_mgr* m, csw_ticket* t);
 
 typedef struct {
@@ -209,21 +213,26 @@ typedef struct {
  * zero-initialise the struct before the first call. */
 csw_status csw_cost_fit(csw_mgr* m, csw_cost_model* model);
 
-/* One candidate tensor of the profiled iteration (the inputs the reference
- * feeds its PolicyMaker: add_tensor / add_comptime, CSWAP+/Execution.h:224-233). */
+/* One swap candidate of the profiled iteration, in forward order (the inputs
+ * the reference feeds its PolicyMaker: add_tensor / add_comptime / add_stepdep,
+ * CSWAP+/Execution.h:224-233). */
 typedef struct {
   size_t numel;
-  double zero_fraction;   /* measured sparsity in [0,1]; <0 if unknown            */
-  int lossy_ok;           /* 1 if ZFP may be applied to this tensor               */
-  double overlap_fwd_s;   /* compute time available to hide the swap-out          */
-  double overlap_bwd_s;   /* compute time available to hide the swap-in           */
+  double zero_fraction;   /* measured sparsity in [0,1]; <0 if unknown              */
+  int lossy_ok;           /* 1 if ZFP may be applied to this tensor                 */
+  double ready_s;         /* forward time (from its start) at which the tensor's
+                             consumer runs, i.e. when its swap-out may begin        */
+  double need_s;          /* backward compute (from its start) that runs before the
+                             tensor is needed again                                 */
 } csw_tensor_desc;
 
-/* Choose per tensor the policy in {RAW, SPARSE, ZFP} with the least exposed
- * time; writes n codes to `policy` and, if non-NULL, the modelled exposed
- * seconds to `exposed`. */
-csw_status csw_cost_decide(const csw_cost_model* model, const csw_tensor_desc* tensors, size_t n, int* policy,
-                           double* exposed);
+/* Choose per tensor a policy in {RAW, SPARSE, ZFP} so that the simulated stall
+ * of one step (serial D2H link in forward order, serial H2D link with one step
+ * of prefetch in backward order, codec times from the model) is smallest;
+ * `fwd_total_s` is the forward pass's compute time.  Writes n codes to `policy`
+ * and, if non-NULL, each tensor's modelled stall in seconds to `exposed`. */
+csw_status csw_cost_decide(const csw_cost_model* model, const csw_tensor_desc* tensors, size_t n, double fwd_total_s,
+                           int* policy, double* exposed);
 
 /* ---- pinned host memory helpers (for callers without a CUDA binding) ------ */
 csw_status csw_host_alloc(size_t bytes, void** p);

@@ -58,20 +58,25 @@ def test_cost_decision_is_pure_host_logic(L):
     cm = cs.CostModel(zfp_enc_b=2.5e-13, zfp_dec_b=2.5e-13, sparse_enc_b=2e-13, sparse_dec_b=1.5e-13,
                       zfp_enc_a=5e-6, zfp_dec_a=5e-6, sparse_enc_a=8e-6, sparse_dec_a=4e-6,
                       d2h_a=1e-5, d2h_bps=50e9, h2d_a=1e-5, h2d_bps=50e9, zfp_maxbits=512)
-    n = 8 << 20
-    pol, exposed = cm.decide([
-        cs.TensorDesc(n, 0.9, False, 0.0, 0.0),
-        cs.TensorDesc(n, 0.0, True, 0.0, 0.0),
-        cs.TensorDesc(n, 0.0, False, 0.0, 0.0),
-        cs.TensorDesc(n, 0.9, True, 1.0, 1.0),
-        cs.TensorDesc(1000, 0.0, True, 0.0, 0.0),
-        cs.TensorDesc(n, -1.0, False, 0.0, 0.0),
-    ])
-    assert pol == [3, 6, 2, 2, 2, 2]
-    assert exposed[1] < exposed[2] and exposed[3] == 0.0
-    # a backlog on the link makes compression worth it even inside a window
-    pol2, _ = cm.decide([cs.TensorDesc(64 << 20, 0.0, False, 1e-4, 1e-4), cs.TensorDesc(n, 0.0, True, 1e-3, 1e-3)])
-    assert pol2 == [2, 6]
+    n = 8 << 20  # 32 MiB tensors: 0.67 ms each on the link, far more than the 1 ms forward pass can hide
+    fwd = 1e-3
+    tensors = [
+        cs.TensorDesc(n, 0.9, False, ready_s=1e-4, need_s=1.8e-3),    # very sparse, lossless only
+        cs.TensorDesc(n, 0.0, True, ready_s=3e-4, need_s=1.4e-3),     # dense, loss allowed
+        cs.TensorDesc(n, 0.0, False, ready_s=5e-4, need_s=1.0e-3),    # dense, lossless: nothing applies
+        cs.TensorDesc(n, -1.0, False, ready_s=7e-4, need_s=0.6e-3),   # sparsity unknown, lossless
+        cs.TensorDesc(n + 8, 0.0, True, ready_s=9e-4, need_s=0.2e-3),  # not a multiple of 1024: no ZFP
+    ]
+    pol, stall = cm.decide(tensors, fwd)
+    assert pol == [3, 6, 2, 2, 2]
+    all_raw = [cs.TensorDesc(t.numel, -1.0, False, t.ready_s, t.need_s) for t in tensors]
+    pol_raw, stall_raw = cm.decide(all_raw, fwd)
+    assert pol_raw == [2] * 5 and sum(stall) < 0.75 * sum(stall_raw)
+    # when the link keeps up with compute nothing stalls and nothing is compressed
+    small = [cs.TensorDesc(1 << 18, 0.9, True, ready_s=1e-4 * i, need_s=1e-3 * (5 - i)) for i in range(5)]
+    pol2, stall2 = cm.decide(small, 1e-3)
+    assert pol2 == [2] * 5 and sum(stall2) == 0.0
+    assert cm.decide([], 0.0) == ([], [])
     with pytest.raises(cs.CswapError):
         cs.CostModel().decide([cs.TensorDesc(n)])  # no link bandwidth fitted
 

@@ -120,19 +120,20 @@ def test_cost_model_fit_and_decide(cs, mgr, tmp_path):
     assert d["d2h_bps"] > 1e9 and d["h2d_bps"] > 1e9
     assert d["zfp_enc_b"] > 0 and d["sparse_enc_b"] > 0
     n = 8 << 20
-    big_window, no_window = 1.0, 0.0
-    pol, exp = cm.decide([
-        cs.TensorDesc(n, zero_fraction=0.9, lossy_ok=False, overlap_fwd_s=no_window, overlap_bwd_s=no_window),
-        cs.TensorDesc(n, zero_fraction=0.0, lossy_ok=True, overlap_fwd_s=no_window, overlap_bwd_s=no_window),
-        cs.TensorDesc(n, zero_fraction=0.0, lossy_ok=False, overlap_fwd_s=no_window, overlap_bwd_s=no_window),
-        cs.TensorDesc(n, zero_fraction=0.9, lossy_ok=True, overlap_fwd_s=big_window, overlap_bwd_s=big_window),
-        cs.TensorDesc(1000, zero_fraction=0.0, lossy_ok=True),
-    ])
+    link_bound = [
+        cs.TensorDesc(n, zero_fraction=0.9, lossy_ok=False, ready_s=1e-4, need_s=1.5e-3),
+        cs.TensorDesc(n, zero_fraction=0.0, lossy_ok=True, ready_s=3e-4, need_s=1.0e-3),
+        cs.TensorDesc(n, zero_fraction=0.0, lossy_ok=False, ready_s=5e-4, need_s=0.5e-3),
+        cs.TensorDesc(1000, zero_fraction=0.0, lossy_ok=True, ready_s=6e-4, need_s=0.1e-3),
+    ]
+    pol, exp = cm.decide(link_bound, 1e-3)
     assert pol[0] == cs.POLICY_SPARSE       # very sparse, lossless only
-    assert pol[1] == cs.POLICY_ZFP          # dense, loss allowed, nothing to hide behind
+    assert pol[1] == cs.POLICY_ZFP          # dense, loss allowed, link saturated
     assert pol[2] == cs.POLICY_RAW          # dense and lossless: nothing helps
-    assert pol[3] == cs.POLICY_RAW          # everything hides behind compute: keep it simple
-    assert pol[4] == cs.POLICY_RAW          # not a multiple of 1024: ZFP not applicable
+    assert pol[3] == cs.POLICY_RAW          # not a multiple of 1024: ZFP not applicable
+    hidden = [cs.TensorDesc(1 << 18, 0.9, True, ready_s=1e-3 * i, need_s=1e-2 * (4 - i)) for i in range(4)]
+    pol_h, exp_h = cm.decide(hidden, 1e-2)
+    assert pol_h == [cs.POLICY_RAW] * 4 and sum(exp_h) == 0.0   # everything hides behind compute
     path = tmp_path / "policy.json"
     cm.save(str(path), pol)
     cm2, pol2 = cs.CostModel.load(str(path))
