@@ -8,7 +8,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libcswap_b200.so")
-SOURCES = ["zfp_kernels.cu", "sparse_kernels.cu", "cswap_abi.cu", "swap_manager.cu", "cost_model.cu"]
+SOURCES = ["zfp_kernels.cu", "sparse_kernels.cu", "cswap_abi.cu", "swap_manager.cu", "cost_model.cu",
+           "sparse_static.cu"]
 HEADERS = ["zfp_core.cuh", "zfp_field.cuh", "zfp_kernels.h", "sparse_kernels.h", "internal.h",
            os.path.join("..", "..", "include", "cswap_b200.h"), os.path.join("..", "..", "include", "cswap_compat.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -78,6 +78,7 @@ const char* csw_status_string(csw_status s) {
     case CSW_ERR_STATE: return "invalid state for this call";
     case CSW_ERR_TIMEOUT: return "bounded device wait ran out";
     case CSW_ERR_UNSUPPORTED: return "unsupported";
+    case CSW_ERR_LIMIT: return "input exceeds the fixed limit of this entry point";
     default: return "unknown status";
   }
 }

@@ -107,6 +107,46 @@ sparse_scan_kernel(uint32_t* __restrict__ tile_off, uint32_t ntiles, uint32_t* _
   if (threadIdx.x == 0) *nnz_out = carry_s;
 }
 
+// Same scan with the counts read from one array and the exclusive offsets
+// written to another (the counts stay untouched).
+__global__ void __launch_bounds__(1024)
+sparse_scan_split_kernel(const uint32_t* __restrict__ tile_cnt, uint32_t* __restrict__ tile_off, uint32_t ntiles,
+                         uint32_t* __restrict__ nnz_out) {
+  __shared__ uint32_t warp_sum[32];
+  __shared__ uint32_t carry_s;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) carry_s = 0;
+  __syncthreads();
+  for (uint32_t base = 0; base < ntiles; base += 1024) {
+    const uint32_t i = base + threadIdx.x;
+    const uint32_t c = i < ntiles ? tile_cnt[i] : 0u;
+    uint32_t x = c;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const uint32_t y = __shfl_up_sync(0xffffffffu, x, d);
+      if (lane >= d) x += y;
+    }
+    if (lane == 31) warp_sum[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+      uint32_t s = warp_sum[lane];
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t y = __shfl_up_sync(0xffffffffu, s, d);
+        if (lane >= d) s += y;
+      }
+      warp_sum[lane] = s;
+    }
+    __syncthreads();
+    const uint32_t carry = carry_s;
+    if (i < ntiles) tile_off[i] = carry + (warp ? warp_sum[warp - 1] : 0u) + x - c;
+    __syncthreads();
+    if (threadIdx.x == 1023) carry_s = carry + warp_sum[31];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) *nnz_out = carry_s;
+}
+
 // ---- pass 3: pack the non-zeros ----------------------------------------------------
 __global__ void __launch_bounds__(kThreads)
 sparse_pack_kernel(const uint32_t* __restrict__ in, uint64_t n, const uint32_t* __restrict__ tile_off,
@@ -288,6 +328,22 @@ cudaError_t sparse_compress_launch(const float* in, uint64_t n, uint32_t* bitmap
     sparse_count_kernel<<<ntiles, kThreads, 0, stream>>>(reinterpret_cast<const uint32_t*>(in), n, bitmap, tile_off);
   }
   sparse_scan_kernel<<<1, 1024, 0, stream>>>(tile_off, ntiles, nnz_out);
+  if (ntiles) {
+    sparse_pack_kernel<<<ntiles, kThreads, 0, stream>>>(reinterpret_cast<const uint32_t*>(in), n, tile_off,
+                                                        reinterpret_cast<uint32_t*>(values));
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t sparse_compress_scratch_launch(const float* in, uint64_t n, uint32_t* bitmap, float* values,
+                                           uint32_t* tile_off, uint32_t* tile_cnt_scratch, uint32_t* nnz_out,
+                                           cudaStream_t stream) {
+  const uint32_t ntiles = (uint32_t)((n + kTile - 1) / kTile);
+  if (ntiles) {
+    sparse_count_kernel<<<ntiles, kThreads, 0, stream>>>(reinterpret_cast<const uint32_t*>(in), n, bitmap,
+                                                         tile_cnt_scratch);
+  }
+  sparse_scan_split_kernel<<<1, 1024, 0, stream>>>(tile_cnt_scratch, tile_off, ntiles, nnz_out);
   if (ntiles) {
     sparse_pack_kernel<<<ntiles, kThreads, 0, stream>>>(reinterpret_cast<const uint32_t*>(in), n, tile_off,
                                                         reinterpret_cast<uint32_t*>(values));

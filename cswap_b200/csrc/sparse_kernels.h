@@ -13,6 +13,11 @@ constexpr int SPARSE_TILE = 4096;  // elements per independently decodable tile
 // *nnz_out (device or mapped host memory) receives the number of values.
 cudaError_t sparse_compress_launch(const float* in, uint64_t n, uint32_t* bitmap, float* values, uint32_t* tile_off,
                                    uint32_t* nnz_out, cudaStream_t stream);
+// Same result, with the per-tile counts kept in a scratch array the caller owns
+// (ceil(n/4096) words) instead of passing through tile_off.
+cudaError_t sparse_compress_scratch_launch(const float* in, uint64_t n, uint32_t* bitmap, float* values,
+                                           uint32_t* tile_off, uint32_t* tile_cnt_scratch, uint32_t* nnz_out,
+                                           cudaStream_t stream);
 cudaError_t sparse_decompress_launch(const uint32_t* bitmap, const float* values, const uint32_t* tile_off, uint64_t n,
                                      float* out, cudaStream_t stream);
 

@@ -43,7 +43,8 @@ enum {
   CSW_ERR_NOMEM = 4,    /* a pool or allocation is exhausted                     */
   CSW_ERR_STATE = 5,    /* call not valid in the handle's current state          */
   CSW_ERR_TIMEOUT = 6,  /* a bounded device-side wait ran out                    */
-  CSW_ERR_UNSUPPORTED = 7
+  CSW_ERR_UNSUPPORTED = 7,
+  CSW_ERR_LIMIT = 8     /* input exceeds a fixed limit of the entry point called  */
 };
 const char* csw_status_string(csw_status s);
 /* cudaError_t of the most recent failing runtime call on this thread (0 if none). */
@@ -115,6 +116,31 @@ csw_status csw_sparse_layout_of(size_t n, csw_sparse_layout* layout);
  * CSWAP+/Execution.h:88-95 without any host round trip. */
 csw_status csw_sparse_compress(const float* d_in, size_t n, void* d_out, size_t cap, uint32_t* nnz_out,
                                csw_stream_t stream);
+/* csw_sparse_compress for callers that must not allocate.  (No counterpart in
+ * the reference, whose swap-out allocates on every call.)
+ *
+ * Meant for code that runs where device allocation is off the table: a swap
+ * hook invoked while the framework's allocator is locked or has just failed
+ * (the moment swapping is most wanted), a callback where cudaMalloc's implicit
+ * synchronisation would stall unrelated streams, or a host program that gets a
+ * fixed memory budget at start-up.  The compressor's per-tile counters sit in
+ * a fixed 256 KiB array inside the library image (present on every GPU that
+ * loads the library until the process exits); the call performs no cudaMalloc,
+ * cudaFree or other allocating call, and writes the same bytes to d_out and
+ * the same count to *nnz_out as csw_sparse_compress.
+ *
+ *  - n may be at most CSW_SPARSE_STATIC_MAX_ELEMS; larger inputs return
+ *    CSW_ERR_LIMIT and launch nothing.
+ *  - The first call on each device looks up the array's device address (a
+ *    runtime query, not an allocation); make that first call outside any
+ *    stream capture.
+ *  - All calls share the one array: two calls whose kernels may run at the same
+ *    time on the same GPU (different streams, no ordering between them) race
+ *    and corrupt each other's output.  Calls ordered on one stream, or by
+ *    events, are fine; nothing needs clearing between them. */
+#define CSW_SPARSE_STATIC_MAX_ELEMS 268435456u /* 65536 tiles of 4096 floats = 1 GiB of input */
+csw_status csw_sparse_compress_static(const float* d_in, size_t n, void* d_out, size_t cap, uint32_t* nnz_out,
+                                      csw_stream_t stream);
 /* Rebuild n floats at d_out from a packed buffer; every element is written
  * (the reference leaves trailing zeros unwritten, compression.cu:281-292). */
 csw_status csw_sparse_decompress(const void* d_in, size_t n, float* d_out, csw_stream_t stream);
