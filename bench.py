@@ -425,8 +425,11 @@ def main():
     peak, peak_kind = load_peaks()
     alg = 4 * n + n * args.rate // 8
     name, t_k = ("zfp_encode_slab_kernel", t_enc) if t_enc >= t_dec else ("zfp_decode_slab_kernel", t_dec)
+    # DRAM read + write bytes of one launch from the committed ncu capture of this exact
+    # workload (profiles/zfp_slab_kernels_256MiB_rate8.md); unknown for other sizes / rates
+    ncu_traffic = {("zfp_encode_slab_kernel", 256, 8): 319.8e6, ("zfp_decode_slab_kernel", 256, 8): 278.2e6}
     roofline = {"bound": "hbm", "kernel": name, "achieved": alg / t_k / 1e9, "peak": peak, "unit": "GB/s",
-                "frac": alg / t_k / 1e9 / peak, "peak_kind": f"of {peak_kind}", "traffic": None,
+                "frac": alg / t_k / 1e9 / peak, "peak_kind": f"of {peak_kind}", "traffic": ncu_traffic.get((name, args.mib, args.rate)),
                 "algorithmic_bytes_per_launch": alg,
                 "encode": {"ms": t_enc * 1e3, "GBps_algorithmic": alg / t_enc / 1e9, "frac": alg / t_enc / 1e9 / peak},
                 "decode": {"ms": t_dec * 1e3, "GBps_algorithmic": alg / t_dec / 1e9, "frac": alg / t_dec / 1e9 / peak},
