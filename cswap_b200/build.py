@@ -53,5 +53,28 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+def build_cpp_driver(force: bool = False) -> str:
+    """Compile tests/cpp/execution_driver.cpp (the C++ Execution class over stock
+    libtorch) against the in-tree library with g++."""
+    import torch
+    root = os.path.dirname(HERE)
+    src = os.path.join(root, "tests", "cpp", "execution_driver.cpp")
+    hdr = os.path.join(root, "include", "cswap_execution.hpp")
+    exe = os.path.join(root, "tests", "cpp", "execution_driver")
+    if not force and os.path.exists(exe) and all(os.path.getmtime(exe) >= os.path.getmtime(f) for f in (src, hdr)):
+        return exe
+    build()
+    t = os.path.dirname(torch.__file__)
+    cuda_inc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
+    cmd = ["g++", "-std=c++17", "-O1", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           "-I", os.path.join(root, "include"), "-I", os.path.join(t, "include"),
+           "-I", os.path.join(t, "include", "torch", "csrc", "api", "include"), "-I", cuda_inc, src, "-o", exe,
+           "-L", os.path.join(t, "lib"), "-L", HERE, f"-Wl,-rpath,{os.path.join(t, 'lib')}",
+           "-Wl,-rpath,$ORIGIN/../../cswap_b200", "-Wl,--no-as-needed",
+           "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda", "-lcswap_b200"]
+    subprocess.check_call(cmd)
+    return exe
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
