@@ -824,4 +824,88 @@ CSW_HD void decode_block(WordSource& src, int maxbits, float (&f)[1 << (2 * DIMS
   for (int i = 0; i < N; i++) f[i] = w * (float)v[i];
 }
 
+// ---- decoder for the slab kernel (3-D blocks, whole words per block) ----------------
+// Same result as decode_block<3>.  Instead of shifting a 64-bit window along
+// the stream (integer-pipe work on every read), the parser keeps one bit
+// position and fetches what it needs from the staged words with two or three
+// shared-memory loads and a funnel shift; the bit budget is simply
+// maxbits - pos.  WordSrc::word(w) returns the block's w-th 32-bit word and 0
+// for the two rows past the end.
+template <class WordSrc>
+CSW_HD uint32_t peek_at(const WordSrc& src, int pos) {
+  const int w = pos >> 5;
+  return funnel_r(src.word(w), src.word(w + 1), pos & 31);
+}
+CSW_HD void or_at(uint32_t& xl, uint32_t& xh, uint32_t pat, int n) {  // x |= pat << n, n in 0..63
+  const int s = n & 31;
+  const uint32_t a = pat << s, b = funnel_l(pat, 0u, s);
+  xl |= n < 32 ? a : 0u;
+  xh |= n < 32 ? b : a;
+}
+
+template <class WordSrc>
+CSW_HD void decode_block3_pos(const WordSrc& src, int maxbits, float (&f)[64], const uint32_t* dec_lut) {
+  const uint32_t head = src.word(0);
+  if (!(head & 1u)) {  // zero block
+#pragma unroll
+    for (int i = 0; i < 64; i++) f[i] = 0.0f;
+    return;
+  }
+  const uint32_t e = (head >> 1) & 0xffu;
+  int pos = 9, n = 0;
+  uint32_t u[64];
+#pragma unroll
+  for (int i = 0; i < 64; i++) u[i] = 0;
+  for (int c = 3; c >= 0; c--) {
+    uint32_t lo[8], hi[8];
+#pragma unroll
+    for (int k = 7; k >= 0; k--) {
+      uint32_t xl = 0u, xh = 0u;
+      if (pos < maxbits) {
+        // first min(n, budget) bits verbatim (decode.cuh:143-145)
+        const int left0 = maxbits - pos;
+        const int m = n < left0 ? n : left0;
+        const int w = pos >> 5, s = pos & 31;
+        const uint32_t w0 = src.word(w), w1 = src.word(w + 1), w2 = src.word(w + 2);
+        xl = funnel_r(w0, w1, s) & low_mask32(m < 32 ? m : 32);
+        xh = funnel_r(w1, w2, s) & low_mask32(m > 32 ? m - 32 : 0);
+        pos += m;
+        // group tests and unary runs (decode.cuh:147-164), up to eight stream bits per step
+        int st = 0;
+        for (;;) {
+          const int left = maxbits - pos;
+          if (st == 1 && (n == 63 || left == 0)) {  // run cut short: the one is implied
+            or_at(xl, xh, 1u, n);
+            n++;
+            st = 0;
+          }
+          if (st == 0 && (n >= 64 || left == 0)) break;
+          const int lim = (st == 0 ? 64 : 63) - n;
+          int L = lim < 8 ? lim : 8;
+          L = left < L ? left : L;
+          const uint32_t en = dec_lut[dec_lut_index(L, st, peek_at(src, pos) & 0xffu)];
+          or_at(xl, xh, (en >> 8) & 0xffu, n);
+          n += (int)((en >> 4) & 0xfu);
+          pos += (int)(en & 0xfu);
+          st = (int)(en >> 16);
+          if (st == 2) break;
+        }
+      }
+      lo[k] = xl;
+      hi[k] = xh;
+    }
+    const uint32_t sel0 = (0x3210u & ~(0xfu << (4 * c))) | (4u << (4 * c));
+    const uint32_t step = 1u << (4 * c);
+    bytes_from_planes<0>(lo, sel0, step, u);
+    bytes_from_planes<1>(hi, sel0, step, u);
+    if (pos >= maxbits) break;
+  }
+  int v[64];
+  inv_order<3>(u, v, std::make_integer_sequence<int, 64>{});
+  inv_xform<3>(v);
+  const float w = dequant_scale(e);
+#pragma unroll
+  for (int i = 0; i < 64; i++) f[i] = w * (float)v[i];
+}
+
 }  // namespace csw

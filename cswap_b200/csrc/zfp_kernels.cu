@@ -11,8 +11,8 @@
 //    is still being coded out of registers; coded words are staged word-major
 //    in shared memory (bank = lane, so diverged lanes never conflict) and
 //    leave as 128-bit coalesced stores.  The decoder stages the compressed
-//    words the same way, rebuilds the slabs in shared memory and writes them
-//    back with one bulk async store per group.
+//    words the same way, parses them by bit position and stores the rebuilt
+//    values straight to global memory (a warp store covers four full lines).
 //  * generic kernels, one thread per block straight from/to global memory, for
 //    any 1-D/2-D/3-D extents, strides, partial blocks and bit budgets.
 //
@@ -72,15 +72,6 @@ __device__ __forceinline__ void bulk_load(void* dst_smem, const void* src, uint3
                "l"(src), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
-// shared -> global bulk async copy (bulk-group completion)
-__device__ __forceinline__ void bulk_store(void* dst, const void* src_smem, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src_smem)),
-               "r"(bytes)
-               : "memory");
-  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-}
-__device__ __forceinline__ void bulk_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // ---- word staging: word w of the block owned by thread t lives at [w * 256 + t] -----
@@ -88,10 +79,11 @@ struct StageSink {
   uint32_t* p;  // &stage[threadIdx.x]
   __device__ __forceinline__ void put(int w, uint32_t v) { p[w * kThreads] = v; }
 };
-struct StageSource {
-  const uint32_t* p;
-  int nwords;
-  __device__ __forceinline__ uint32_t get(int w) const { return w < nwords ? p[w * kThreads] : 0u; }
+// Staged stream words of the decoder: rows nwords and nwords + 1 are kept zero
+// so that reads just past a block need no bounds test.
+struct StageWords {
+  const uint32_t* p;  // &stage[threadIdx.x]
+  __device__ __forceinline__ uint32_t word(int w) const { return p[w * kThreads]; }
 };
 
 // Staged words and the per-lane expansion queue of the staged encoder, both
@@ -234,18 +226,17 @@ __global__ void __launch_bounds__(kThreads, 2)
 zfp_decode_slab_kernel(const uint32_t* __restrict__ in, float* __restrict__ out, uint32_t nz, int maxbits,
                        int* __restrict__ status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  float* tile = reinterpret_cast<float*>(smem_raw);
-  uint32_t* stage = reinterpret_cast<uint32_t*>(smem_raw + kGroupBytes);
+  uint32_t* stage = reinterpret_cast<uint32_t*>(smem_raw);
   const int nwords = maxbits >> 5;
-  uint32_t* lut = stage + nwords * kThreads;
+  uint32_t* lut = stage + (nwords + STAGE_SPARE_ROWS) * kThreads;
   (void)status;
 
   const int tid = threadIdx.x;
   for (int i = tid; i < DEC_LUT_SIZE; i += kThreads) lut[i] = dec_lut_entry(i);
+  for (int w = nwords; w < nwords + STAGE_SPARE_ROWS; w++) stage[w * kThreads + tid] = 0u;
 
   const uint32_t ngroups = (nz + kGroupSlabs - 1) / kGroupSlabs;
   const int t = tid >> 6, bx = tid & 7, by = (tid >> 3) & 7;
-  float* my = tile + t * 4 * kSlabFloats + by * 128 + bx * 4;
 
   for (uint32_t g = blockIdx.x; g < ngroups; g += gridDim.x) {
     // stage the group's compressed words, word-major
@@ -270,31 +261,28 @@ zfp_decode_slab_kernel(const uint32_t* __restrict__ in, float* __restrict__ out,
         stage[w * kThreads + b] = __ldg(src + q);
       }
     }
-    // the previous group's bulk store must have finished reading the tile
-    if (tid == 0) bulk_store_wait_read();
     __syncthreads();
 
     const uint32_t zt = g * kGroupSlabs + t * 4;
     if (zt < nz) {
       float f[64];
-      StageSource source{stage + tid, nwords};
-      decode_block<3>(source, maxbits, f, lut);
+      StageWords source{stage + tid};
+      decode_block3_pos(source, maxbits, f, lut);
+      // eight neighbouring lanes cover one 128-byte row segment, so every store
+      // instruction of a warp writes four full lines: no staging of the output
+      const int vz = nz - zt < 4 ? (int)(nz - zt) : 4;
+      float* dst = out + (size_t)zt * kSlabFloats + by * 128 + bx * 4;
 #pragma unroll
       for (int z = 0; z < 4; z++)
+        if (z < vz) {
 #pragma unroll
-        for (int y = 0; y < 4; y++)
-          *reinterpret_cast<float4*>(my + z * kSlabFloats + y * 32) =
-              make_float4(f[16 * z + 4 * y], f[16 * z + 4 * y + 1], f[16 * z + 4 * y + 2], f[16 * z + 4 * y + 3]);
+          for (int y = 0; y < 4; y++)
+            *reinterpret_cast<float4*>(dst + z * kSlabFloats + y * 32) =
+                make_float4(f[16 * z + 4 * y], f[16 * z + 4 * y + 1], f[16 * z + 4 * y + 2], f[16 * z + 4 * y + 3]);
+        }
     }
-    fence_async_smem();  // make the generic-proxy writes visible to the bulk copy
-    __syncthreads();
-    if (tid == 0) {
-      const uint32_t z0 = g * kGroupSlabs;
-      const uint32_t slabs = nz - z0 < (uint32_t)kGroupSlabs ? nz - z0 : (uint32_t)kGroupSlabs;
-      bulk_store(out + (size_t)z0 * kSlabFloats, tile, slabs * kSlabFloats * 4);
-    }
+    __syncthreads();  // the staged words are free for the next group
   }
-  if (tid == 0) bulk_store_wait_all();
 }
 
 // =====================================================================================
@@ -375,7 +363,8 @@ zfp_decode_generic_kernel(FieldGeom g, const uint32_t* __restrict__ in, float* _
 // launchers
 // =====================================================================================
 static size_t slab_smem_bytes(int maxbits, bool decode) {
-  if (decode) return (size_t)kGroupBytes + (size_t)(maxbits >> 5) * kThreads * 4 + DEC_LUT_SIZE * 4;
+  if (decode)
+    return (size_t)((maxbits >> 5) + STAGE_SPARE_ROWS) * kThreads * 4 + DEC_LUT_SIZE * 4;
   const int queue_rows = encode_queue_in_tile(maxbits) ? 0 : QUEUE_SLOTS * QUEUE_FIELDS;
   return (size_t)kGroupBytes + (size_t)((maxbits >> 5) + STAGE_SPARE_ROWS + queue_rows) * kThreads * 4 +
          ENC_LUT_SIZE * 4;

@@ -84,6 +84,24 @@ void core_encode_staged(const float* in, size_t nx, size_t ny, size_t nz, int ma
     for (int i = 0; i < nw; i++) out[b * nw + i] = rows[i];
   }
 }
+// the slab kernel's position-based decoder
+struct PadSource {
+  const uint32_t* w;
+  int n;
+  uint32_t word(int i) const { return i < n ? w[i] : 0u; }
+};
+void core_decode_pos(const uint32_t* in, size_t nx, size_t ny, size_t nz, int maxbits, float* out) {
+  csw::FieldGeom g = csw::make_geom(nx, ny, nz, 0, 0, 0);
+  auto lut = dec_lut();
+  const int nw = maxbits / 32;
+  size_t nb = csw::geom_blocks(g);
+  for (size_t b = 0; b < nb; b++) {
+    float q[64];
+    PadSource s{in + b * nw, nw};
+    csw::decode_block3_pos(s, maxbits, q, lut.data());
+    csw::scatter_block<3>(g, out, b, q);
+  }
+}
 // maxbits must be a multiple of 32 here (whole words per block)
 void core_encode(const float* in, size_t nx, size_t ny, size_t nz, int maxbits, uint32_t* out) {
   csw::FieldGeom g = csw::make_geom(nx, ny, nz, 0, 0, 0);

@@ -46,6 +46,11 @@ def _run(core, O, a, dims, maxbits):
     core.core_decode(inw.ctypes.data_as(C.c_void_p), C.c_size_t(nx), C.c_size_t(ny), C.c_size_t(nz), maxbits,
                      d2.ctypes.data_as(C.c_void_p))
     assert np.array_equal(d.view(np.uint32), d2.view(np.uint32))
+    if nz:  # the slab kernel's position-based decoder
+        d3 = np.zeros(a.size, dtype=np.float32)
+        core.core_decode_pos(inw.ctypes.data_as(C.c_void_p), C.c_size_t(nx), C.c_size_t(ny), C.c_size_t(nz), maxbits,
+                             d3.ctypes.data_as(C.c_void_p))
+        assert np.array_equal(d.view(np.uint32), d3.view(np.uint32))
 
 
 @pytest.mark.parametrize("dims", [(32, 32, 16), (32, 32, 7), (9, 5, 3), (4, 4, 4), (13, 0, 0), (64, 0, 0),
