@@ -297,6 +297,99 @@ bool contiguous(const csw_zfp_field* f) {
 }
 size_t field_values(const csw_zfp_field* f) { return f->nx * (f->ny ? f->ny : 1) * (f->nz ? f->nz : 1); }
 
+// Host-to-host calls on large 3-D fields are cut into z-chunks (zfp blocks are
+// independent, so chunk streams concatenate exactly) and run as a three-stage
+// pipeline - host->device copy, codec, device->host copy - on three streams, so
+// that both directions of the host link are busy at once.
+struct Pipeline {
+  cudaStream_t in = nullptr, work = nullptr, out = nullptr;
+  static constexpr int kMaxChunks = 64;
+  cudaEvent_t loaded[kMaxChunks] = {}, coded[kMaxChunks] = {};
+  int dev = -1;
+  cudaError_t prepare() {
+    int d = 0;
+    cudaError_t e = cudaGetDevice(&d);
+    if (e != cudaSuccess || d == dev) return e;
+    if (dev >= 0) return cudaErrorInvalidDevice;  // created for another device: use the plain path
+    e = cudaStreamCreateWithFlags(&in, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&work, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&out, cudaStreamNonBlocking);
+    for (int i = 0; i < kMaxChunks && e == cudaSuccess; i++) {
+      e = cudaEventCreateWithFlags(&loaded[i], cudaEventDisableTiming);
+      if (e == cudaSuccess) e = cudaEventCreateWithFlags(&coded[i], cudaEventDisableTiming);
+    }
+    if (e == cudaSuccess) dev = d;
+    return e;
+  }
+};
+Pipeline g_pipe;
+
+// true when the call was handled here (ok tells how it went)
+bool pipelined_host_call(bool compress, const csw_zfp_field* f, void* h_stream, unsigned maxbits, size_t bytes,
+                         bool* ok) {
+  const size_t slab = f->nx * f->ny;                      // values per z-slab
+  const size_t blocks_per_4 = ((f->nx + 3) / 4) * ((f->ny + 3) / 4);
+  if (f->nz < 64 || maxbits % 64 || !contiguous(f) || slab * f->nz * 4 < (size_t(64) << 20)) return false;
+  // chunk: a multiple of 4 slabs close to 32 MiB of field
+  size_t zc = (size_t(32) << 20) / (slab * 4);
+  zc = zc < 4 ? 4 : zc / 4 * 4;
+  const size_t nchunks = (f->nz + zc - 1) / zc;
+  if (nchunks < 2 || nchunks > Pipeline::kMaxChunks) return false;
+  if (g_pipe.prepare() != cudaSuccess) { cudaGetLastError(); return false; }
+  const size_t fb = slab * f->nz * 4;
+  if (g_field_stage.reserve(fb) != cudaSuccess || g_stream_stage.reserve(bytes) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  *ok = false;
+  cudaError_t e = cudaStreamSynchronize(nullptr);  // earlier default-stream work (as the reference's device sync)
+  char* h_field = static_cast<char*>(f->data);
+  char* d_field = static_cast<char*>(g_field_stage.p);
+  char* d_stream = static_cast<char*>(g_stream_stage.p);
+  char* hs = static_cast<char*>(h_stream);
+  for (size_t c = 0; c < nchunks && e == cudaSuccess; c++) {
+    const size_t z0 = c * zc, nzc = f->nz - z0 < zc ? f->nz - z0 : zc;
+    const size_t foff = z0 * slab * 4, flen = nzc * slab * 4;
+    const size_t soff = (z0 / 4) * blocks_per_4 * maxbits / 8;
+    size_t slen = 0;
+    csw_zfp_max_bytes(f->nx, f->ny, nzc, maxbits, &slen);
+    csw_status st;
+    if (compress) {
+      e = cudaMemcpyAsync(d_field + foff, h_field + foff, flen, cudaMemcpyHostToDevice, g_pipe.in);
+      if (e == cudaSuccess) e = cudaEventRecord(g_pipe.loaded[c], g_pipe.in);
+      if (e == cudaSuccess) e = cudaStreamWaitEvent(g_pipe.work, g_pipe.loaded[c], 0);
+      if (e != cudaSuccess) break;
+      st = csw_zfp_compress(reinterpret_cast<const float*>(d_field + foff), f->nx, f->ny, nzc, maxbits,
+                            d_stream + soff, slen, nullptr, g_pipe.work);
+      if (st != CSW_OK) return true;
+      e = cudaEventRecord(g_pipe.coded[c], g_pipe.work);
+      if (e == cudaSuccess) e = cudaStreamWaitEvent(g_pipe.out, g_pipe.coded[c], 0);
+      if (e == cudaSuccess) e = cudaMemcpyAsync(hs + soff, d_stream + soff, slen, cudaMemcpyDeviceToHost, g_pipe.out);
+    } else {
+      e = cudaMemcpyAsync(d_stream + soff, hs + soff, slen, cudaMemcpyHostToDevice, g_pipe.in);
+      if (e == cudaSuccess) e = cudaEventRecord(g_pipe.loaded[c], g_pipe.in);
+      if (e == cudaSuccess) e = cudaStreamWaitEvent(g_pipe.work, g_pipe.loaded[c], 0);
+      if (e != cudaSuccess) break;
+      st = csw_zfp_decompress(d_stream + soff, slen, f->nx, f->ny, nzc, maxbits,
+                              reinterpret_cast<float*>(d_field + foff), g_pipe.work);
+      if (st != CSW_OK) return true;
+      e = cudaEventRecord(g_pipe.coded[c], g_pipe.work);
+      if (e == cudaSuccess) e = cudaStreamWaitEvent(g_pipe.out, g_pipe.coded[c], 0);
+      if (e == cudaSuccess) e = cudaMemcpyAsync(h_field + foff, d_field + foff, flen, cudaMemcpyDeviceToHost, g_pipe.out);
+    }
+  }
+  if (e == cudaSuccess) e = cudaStreamSynchronize(g_pipe.out);
+  if (e != cudaSuccess) {
+    legacy_report(compress ? "cuda_compress" : "cuda_decompress", e);
+    cudaStreamSynchronize(g_pipe.in);
+    cudaStreamSynchronize(g_pipe.work);
+    cudaStreamSynchronize(g_pipe.out);
+    return true;
+  }
+  *ok = true;
+  return true;
+}
+
 }  // namespace
 
 size_t cuda_compress(csw_zfp_stream* zs, const csw_zfp_field* f) {
@@ -310,6 +403,15 @@ size_t cuda_compress(csw_zfp_stream* zs, const csw_zfp_field* f) {
   size_t bytes = 0;
   if (csw_zfp_max_bytes(f->nx, f->ny, f->nz, maxbits, &bytes) != CSW_OK) return 0;
   const bool field_dev = is_device_ptr(f->data), stream_dev = is_device_ptr(zs->stream->begin);
+  if (!field_dev && !stream_dev) {
+    bool ok = false;
+    if (pipelined_host_call(true, f, zs->stream->begin, maxbits, bytes, &ok)) {
+      if (!ok) return 0;
+      zs->stream->bits = 64;
+      zs->stream->ptr = zs->stream->begin + bytes / 8;
+      return bytes;
+    }
+  }
   const float* d_field = static_cast<const float*>(f->data);
   ptrdiff_t sx = f->sx, sy = f->sy, sz = f->sz;
   if (!field_dev) {
@@ -351,6 +453,16 @@ void cuda_decompress(csw_zfp_stream* zs, csw_zfp_field* f) {
   size_t bytes = 0;
   if (csw_zfp_max_bytes(f->nx, f->ny, f->nz, maxbits, &bytes) != CSW_OK) return;
   const bool field_dev = is_device_ptr(f->data), stream_dev = is_device_ptr(zs->stream->begin);
+  if (!field_dev && !stream_dev) {
+    bool ok = false;
+    if (pipelined_host_call(false, f, zs->stream->begin, maxbits, bytes, &ok)) {
+      if (ok) {
+        zs->stream->bits = 64;
+        zs->stream->ptr = zs->stream->begin + bytes / 8;
+      }
+      return;
+    }
+  }
   float* d_field = static_cast<float*>(f->data);
   ptrdiff_t sx = f->sx, sy = f->sy, sz = f->sz;
   const size_t fb = field_values(f) * sizeof(float);

@@ -224,3 +224,33 @@ def test_reference_named_entry_points(cs, oracle, where):
     L.cuda_decompress(C.byref(zs2), C.byref(fld))
     back = field_buf if where == "host" else ft.cpu().numpy()
     assert np.array_equal(back, oracle.zfp_decode(ref, nx, ny, nz, maxbits))
+
+
+def test_large_host_call_is_pipelined_and_exact(cs):
+    """Host field + host stream of 100 MiB: cuda_compress / cuda_decompress cut
+    the field into z-chunks and overlap copies with coding; the bytes must be
+    the ones the one-shot device path produces (nz deliberately ragged)."""
+    import torch
+    from cswap_b200._lib import Bitstream, ZfpField, ZfpStream
+    nx, ny, nz, maxbits = 32, 32, 25601 + 2, 512
+    n = nx * ny * nz
+    t = torch.tanh(torch.randn(n, device="cuda", generator=torch.Generator(device="cuda").manual_seed(3)))
+    want = cs.zfp_compress(t, maxbits, (nx, ny, nz))
+    want_back = cs.zfp_decompress(want, n, maxbits, (nx, ny, nz))
+    nbytes = cs.zfp_max_bytes(nx, ny, nz, maxbits)
+    h_field = t.cpu().pin_memory()
+    h_stream = torch.zeros(nbytes, dtype=torch.uint8).pin_memory()
+    L = cs.lib()
+    sp = h_stream.data_ptr()
+    bs = Bitstream(0, 0, sp, sp, sp + nbytes)
+    zs = ZfpStream(maxbits, maxbits, 32, -1074, C.pointer(bs))
+    fld = ZfpField(3, nx, ny, nz, 0, 0, 0, 0, 0, h_field.data_ptr())
+    assert L.cuda_compress(C.byref(zs), C.byref(fld)) == nbytes
+    assert torch.equal(h_stream, want.cpu())
+    h_out = torch.zeros(n, dtype=torch.float32).pin_memory()
+    bs2 = Bitstream(0, 0, sp, sp, sp + nbytes)
+    zs2 = ZfpStream(maxbits, maxbits, 32, -1074, C.pointer(bs2))
+    fld2 = ZfpField(3, nx, ny, nz, 0, 0, 0, 0, 0, h_out.data_ptr())
+    L.cuda_decompress(C.byref(zs2), C.byref(fld2))
+    assert bs2.ptr == sp + nbytes
+    assert torch.equal(h_out, want_back.cpu())
