@@ -643,16 +643,9 @@ CSW_HD void encode_block3_staged(const float (&f)[64], int maxbits, Stage& st, c
     int count = 0;
 #pragma unroll
     for (int k = 7; k >= 0; k--) {
-      const bool live = off < maxbits;
-      if (warp_all(!live || sg.n >= 64)) {
-        // every lane of the warp copies the plane verbatim (or is finished)
-        if (live) {
-          stage_put64(st, off, lo[k], hi[k]);
-          off += 64;
-        }
-      } else if (live) {
-        // n < 64 on some lane: one predicated path for all of them.  With
-        // n == 64 the masks select the whole word and nothing is left over.
+      if (off < maxbits) {
+        // one path for every lane: with n == 64 the masks select the whole
+        // word, no position is left over and no group test is coded
         const int n = sg.n, s = n & 31;
         const uint32_t fl = funnel_r(lo[k], hi[k], s), sh = hi[k] >> s;
         const uint32_t xl = n >= 64 ? 0u : (n < 32 ? fl : sh);
