@@ -100,8 +100,6 @@ struct SmemStage {
   }
 };
 
-__host__ __device__ constexpr bool encode_queue_in_tile(int maxbits) { return maxbits > 768; }
-
 // z-slab that feeds row z of a block with vz valid slabs (encode.cuh:17-38
 // applied along z: a,a,a,a / a,b,b,a / a,b,c,a)
 __device__ __forceinline__ int pad_src_z(int z, int vz) { return z < vz ? z : (z == 3 ? 0 : vz - 1); }
@@ -111,111 +109,58 @@ __device__ __forceinline__ int pad_src_z(int z, int vz) { return z < vz ? z : (z
 // =====================================================================================
 // slab encoder
 // =====================================================================================
+// One CTA per group of 16 z-slabs (256 blocks, lane = block).  A lane reads its
+// 4x4x4 block with sixteen 128-bit loads (eight neighbouring lanes cover one
+// 128-byte row segment, so a warp load touches four full lines), codes it into
+// its own column of the word-major staging area and writes its own words out:
+// after the table is built no warp waits for another.
 __global__ void __launch_bounds__(kThreads, 2)
 zfp_encode_slab_kernel(const float* __restrict__ in, uint32_t* __restrict__ out, uint32_t nz, int maxbits,
-                       int* __restrict__ status, const PipeConsts kc) {
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-  float* tile = reinterpret_cast<float*>(smem_raw);
-  uint32_t* stage = reinterpret_cast<uint32_t*>(smem_raw + kGroupBytes);
+                       const PipeConsts kc) {
+  extern __shared__ __align__(16) uint32_t smem_words[];
   const int nwords = maxbits >> 5;
-  // At high rates the staged words leave no room for a separate expansion queue
-  // if two CTAs are to share an SM: the queue then lives in the tile buffer and
-  // the next group's copy is issued only after coding (the other CTA covers it).
-  const bool queue_in_tile = encode_queue_in_tile(maxbits);
-  uint32_t* after_stage = stage + (nwords + STAGE_SPARE_ROWS) * kThreads;
-  uint32_t* queue = queue_in_tile ? reinterpret_cast<uint32_t*>(tile) : after_stage;
-  uint32_t* lut = queue_in_tile ? after_stage : after_stage + QUEUE_SLOTS * QUEUE_FIELDS * kThreads;
-  __shared__ __align__(8) uint64_t bar;
+  uint32_t* stage = smem_words;
+  uint32_t* queue = stage + (nwords + STAGE_SPARE_ROWS) * kThreads;
+  uint32_t* lut = queue + QUEUE_SLOTS * QUEUE_FIELDS * kThreads;
 
   const int tid = threadIdx.x;
+  // my block: tile t of the group (4 slabs), block (bx, by) of its 8x8 grid
+  const int t = tid >> 6, bx = tid & 7, by = (tid >> 3) & 7;
+  const uint32_t zt = (blockIdx.x * 4 + t) * 4;  // first slab of my tile
+  const int vz = zt >= nz ? 0 : (nz - zt < 4 ? (int)(nz - zt) : 4);
+  float f[64];
+  if (vz > 0) {
+    const float* my = in + (size_t)zt * kSlabFloats + by * 128 + bx * 4;
+#pragma unroll
+    for (int z = 0; z < 4; z++) {
+      const float* row = my + pad_src_z(z, vz) * kSlabFloats;
+#pragma unroll
+      for (int y = 0; y < 4; y++) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(row + y * 32));
+        f[16 * z + 4 * y + 0] = v.x;
+        f[16 * z + 4 * y + 1] = v.y;
+        f[16 * z + 4 * y + 2] = v.z;
+        f[16 * z + 4 * y + 3] = v.w;
+      }
+    }
+  }
   lut[tid] = enc_lut_entry((uint32_t)tid);
   for (int w = 0; w < nwords; w++) stage[w * kThreads + tid] = 0u;  // coded bits are OR-ed in
-  if (tid == 0) {
-    mbar_init(&bar, 1);
-    fence_async_smem();
-  }
-  __syncthreads();
+  __syncthreads();  // the table is complete
+  if (vz == 0) return;
 
-  const uint32_t ngroups = (nz + kGroupSlabs - 1) / kGroupSlabs;
-  uint32_t parity = 0;
-  auto issue = [&](uint32_t g) {
-    const uint32_t z0 = g * kGroupSlabs;
-    const uint32_t slabs = nz - z0 < (uint32_t)kGroupSlabs ? nz - z0 : (uint32_t)kGroupSlabs;
-    mbar_expect_tx(&bar, slabs * kSlabFloats * 4);
-    bulk_load(tile, in + (size_t)z0 * kSlabFloats, slabs * kSlabFloats * 4, &bar);
-  };
-  uint32_t g = blockIdx.x;
-  if (tid == 0 && g < ngroups) issue(g);
+  SmemStage st{stage + tid, queue + tid};
+  encode_block3_staged(f, maxbits, st, lut, kc);
 
-  // my block inside the group: tile t (4 slabs), block (bx, by) of its 8x8 grid
-  const int t = tid >> 6, bx = tid & 7, by = (tid >> 3) & 7;
-  const float* my = tile + t * 4 * kSlabFloats + by * 128 + bx * 4;
-
-  for (; g < ngroups; g += gridDim.x) {
-    const bool landed = mbar_wait(&bar, parity);
-    parity ^= 1;
-    if (!__syncthreads_and(landed)) {
-      // give the copy one more bounded chance to land before leaving
-      if (!landed) mbar_wait(&bar, parity ^ 1);
-      if (tid == 0) atomicExch(status, CSW_KERNEL_TIMEOUT);
-      return;
-    }
-    const uint32_t zt = g * kGroupSlabs + t * 4;  // first slab of my tile
-    const int vz = zt >= nz ? 0 : (nz - zt < 4 ? (int)(nz - zt) : 4);
-    float f[64];
-    if (vz > 0) {
-#pragma unroll
-      for (int z = 0; z < 4; z++) {
-        const float* row = my + pad_src_z(z, vz) * kSlabFloats;
-#pragma unroll
-        for (int y = 0; y < 4; y++) {
-          const float4 v = *reinterpret_cast<const float4*>(row + y * 32);
-          f[16 * z + 4 * y + 0] = v.x;
-          f[16 * z + 4 * y + 1] = v.y;
-          f[16 * z + 4 * y + 2] = v.z;
-          f[16 * z + 4 * y + 3] = v.w;
-        }
-      }
-    }
-    __syncthreads();  // every lane holds its block: the tile may be overwritten
-    if (!queue_in_tile && tid == 0 && g + gridDim.x < ngroups) issue(g + gridDim.x);
-
-    if (vz > 0) {
-      SmemStage st{stage + tid, queue + tid};
-      encode_block3_staged(f, maxbits, st, lut, kc);
-    }
-    __syncthreads();
-    if (queue_in_tile && tid == 0 && g + gridDim.x < ngroups) issue(g + gridDim.x);
-
-    // coalesced write-out of the group's blocks (block-major, nwords each)
-    const uint32_t tiles = ((nz + 3) >> 2) - g * 4 < 4 ? ((nz + 3) >> 2) - g * 4 : 4;
-    const uint32_t nblk = tiles * 64;
-    uint32_t* dst = out + (size_t)g * kThreads * nwords;
-    if ((nwords & 3) == 0) {
-      const uint32_t per = nwords >> 2, chunks = nblk * per;
-      for (uint32_t q = tid; q < chunks; q += kThreads) {
-        const uint32_t b = q / per, c = q - b * per;
-        uint32_t* s = stage + (4 * c) * kThreads + b;
-        uint4 v;
-        v.x = s[0];
-        v.y = s[kThreads];
-        v.z = s[2 * kThreads];
-        v.w = s[3 * kThreads];
-        s[0] = 0u;  // ready for the next group
-        s[kThreads] = 0u;
-        s[2 * kThreads] = 0u;
-        s[3 * kThreads] = 0u;
-        reinterpret_cast<uint4*>(dst)[q] = v;
-      }
-    } else {
-      const uint32_t words = nblk * nwords;
-      for (uint32_t q = tid; q < words; q += kThreads) {
-        const uint32_t b = q / nwords, w = q - b * nwords;
-        dst[q] = stage[w * kThreads + b];
-        stage[w * kThreads + b] = 0u;
-      }
-    }
-    // the next iteration writes `stage` only after its own first barrier
+  // a lane's words sit in its own column: no barrier before reading them back
+  uint32_t* dst = out + ((size_t)blockIdx.x * kThreads + tid) * nwords;
+  const uint32_t* col = stage + tid;
+  if ((nwords & 3) == 0) {
+    for (int w = 0; w < nwords; w += 4)
+      *reinterpret_cast<uint4*>(dst + w) = make_uint4(col[w * kThreads], col[(w + 1) * kThreads],
+                                                      col[(w + 2) * kThreads], col[(w + 3) * kThreads]);
+  } else {
+    for (int w = 0; w < nwords; w++) dst[w] = col[w * kThreads];
   }
 }
 
@@ -365,9 +310,7 @@ zfp_decode_generic_kernel(FieldGeom g, const uint32_t* __restrict__ in, float* _
 static size_t slab_smem_bytes(int maxbits, bool decode) {
   if (decode)
     return (size_t)((maxbits >> 5) + STAGE_SPARE_ROWS) * kThreads * 4 + DEC_LUT_SIZE * 4;
-  const int queue_rows = encode_queue_in_tile(maxbits) ? 0 : QUEUE_SLOTS * QUEUE_FIELDS;
-  return (size_t)kGroupBytes + (size_t)((maxbits >> 5) + STAGE_SPARE_ROWS + queue_rows) * kThreads * 4 +
-         ENC_LUT_SIZE * 4;
+  return (size_t)((maxbits >> 5) + STAGE_SPARE_ROWS + QUEUE_SLOTS * QUEUE_FIELDS) * kThreads * 4 + ENC_LUT_SIZE * 4;
 }
 
 bool zfp_slab_eligible(const FieldGeom& g, const void* field, const void* stream, int maxbits) {
@@ -390,8 +333,9 @@ cudaError_t zfp_encode_launch(const FieldGeom& g, const float* in, void* out, in
     cudaError_t e = cudaFuncSetAttribute(zfp_encode_slab_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)slab_smem_bytes(2048, false));
     if (e != cudaSuccess) return e;
-    zfp_encode_slab_kernel<<<slab_grid(g.nz, 2 * sm_count), kThreads, smem, stream>>>(
-        in, reinterpret_cast<uint32_t*>(out), g.nz, maxbits, d_status, pipe_consts());
+    const uint32_t ngroups = (g.nz + kGroupSlabs - 1) / kGroupSlabs;
+    zfp_encode_slab_kernel<<<ngroups, kThreads, smem, stream>>>(in, reinterpret_cast<uint32_t*>(out), g.nz, maxbits,
+                                                               pipe_consts());
     return cudaGetLastError();
   }
   if (maxbits & 31) {
