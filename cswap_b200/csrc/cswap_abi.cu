@@ -137,11 +137,7 @@ csw_status csw_zfp_compress_strided(const float* d_in, size_t nx, size_t ny, siz
   const size_t need = stream_bytes(g, maxbits);
   if (bytes) *bytes = need;
   if (cap < need) return CSW_ERR_SIZE;
-  int sms = 0;
-  int* d_status = nullptr;
-  st = device_state(&sms, &d_status);
-  if (st != CSW_OK) return st;
-  cudaError_t e = zfp_encode_launch(g, d_in, d_out, (int)maxbits, sms, d_status, stream);
+  cudaError_t e = zfp_encode_launch(g, d_in, d_out, (int)maxbits, stream);
   return e == cudaSuccess ? CSW_OK : cuda_fail(e);
 }
 
@@ -158,11 +154,7 @@ csw_status csw_zfp_decompress_strided(const void* d_in, size_t bytes, size_t nx,
   if (!d_in || !d_out) return CSW_ERR_ARG;
   const FieldGeom g = make_geom(nx, ny, nz, sx, sy, sz);
   if (bytes < stream_bytes(g, maxbits)) return CSW_ERR_SIZE;
-  int sms = 0;
-  int* d_status = nullptr;
-  st = device_state(&sms, &d_status);
-  if (st != CSW_OK) return st;
-  cudaError_t e = zfp_decode_launch(g, d_in, d_out, (int)maxbits, sms, d_status, stream);
+  cudaError_t e = zfp_decode_launch(g, d_in, d_out, (int)maxbits, stream);
   return e == cudaSuccess ? CSW_OK : cuda_fail(e);
 }
 

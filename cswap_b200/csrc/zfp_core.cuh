@@ -292,7 +292,7 @@ CSW_HD void bytes_from_planes(uint32_t (&p)[8], uint32_t sel0, uint32_t step, ui
 // (positions up to the top set bit, plus one per set bit; the final group-test
 // bit is then the '0' terminator).
 constexpr int ENC_LUT_SIZE = 256;
-CSW_HD uint32_t enc_lut_entry(uint32_t v) {
+constexpr CSW_HD uint32_t enc_lut_entry(uint32_t v) {
   uint32_t pat = 0;
   int len = 0, top = -1, ones = 0;
   for (int i = 0; i < 8; i++) {
@@ -317,8 +317,8 @@ CSW_HD uint32_t enc_lut_entry(uint32_t v) {
 // bits 8..15: plane bits found, relative to the starting position;
 // bits 16..17: state afterwards.
 constexpr int DEC_LUT_SIZE = 8 * 2 * 256;
-CSW_HD int dec_lut_index(int L, int state, uint32_t byte) { return ((L - 1) * 2 + state) * 256 + (int)byte; }
-CSW_HD uint32_t dec_lut_entry(int idx) {
+constexpr CSW_HD int dec_lut_index(int L, int state, uint32_t byte) { return ((L - 1) * 2 + state) * 256 + (int)byte; }
+constexpr CSW_HD uint32_t dec_lut_entry(int idx) {
   uint32_t byte = idx & 255;
   int st = (idx >> 8) & 1, L = (idx >> 9) + 1;
   int c = 0, dn = 0;

@@ -53,7 +53,10 @@ int csw_last_cuda_error(void);
 const char* csw_version(void);
 /* Reads (and clears) the device-side status word of the current device:
  * CSW_OK, or CSW_ERR_TIMEOUT if a kernel gave up on a bounded wait.
- * Synchronises `stream` first. */
+ * Synchronises `stream` first.  The kernels of this version contain no
+ * device-side wait (no kernel depends on another CTA, a flag or a copy in
+ * flight), so the word stays zero; the call remains as the place where such a
+ * failure would surface. */
 csw_status csw_device_status(csw_stream_t stream);
 
 /* ---- 2. ZFP fixed-rate float32 ------------------------------------------- */
