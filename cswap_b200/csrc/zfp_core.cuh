@@ -313,9 +313,10 @@ constexpr CSW_HD uint32_t enc_lut_entry(uint32_t v) {
 // group-test parser of decode.cuh:147-164 over at most L stream bits.
 // State 0: expecting a group-test bit; state 1: inside a unary run (expecting
 // value bits until a one); state 2: negative group test seen, plane finished.
-// bits 0..3: stream bits consumed; bits 4..7: positions advanced;
-// bits 8..15: plane bits found, relative to the starting position;
-// bits 16..17: state afterwards.
+// One field per byte, so that each is a single byte-permute away:
+// byte 0: stream bits consumed; byte 1: positions advanced;
+// byte 2: plane bits found, relative to the starting position;
+// byte 3: state afterwards.
 constexpr int DEC_LUT_SIZE = 8 * 2 * 256;
 constexpr CSW_HD int dec_lut_index(int L, int state, uint32_t byte) { return ((L - 1) * 2 + state) * 256 + (int)byte; }
 constexpr CSW_HD uint32_t dec_lut_entry(int idx) {
@@ -334,22 +335,26 @@ constexpr CSW_HD uint32_t dec_lut_entry(int idx) {
       dn++;
     }
   }
-  return (uint32_t)c | ((uint32_t)dn << 4) | (pat << 8) | ((uint32_t)st << 16);
+  return (uint32_t)c | ((uint32_t)dn << 8) | (pat << 16) | ((uint32_t)st << 24);
 }
+CSW_HD int dec_lut_used(uint32_t e) { return (int)(e & 0xffu); }
+CSW_HD int dec_lut_advance(uint32_t e) { return (int)byte_perm(e, 0u, 0x4441u); }
+CSW_HD uint32_t dec_lut_pattern(uint32_t e) { return byte_perm(e, 0u, 0x4442u); }
+CSW_HD int dec_lut_state(uint32_t e) { return (int)(e >> 24); }
 
 // ---- bit emitter ------------------------------------------------------------------
 // WordSink::put(w, word) receives the block's w-th 32-bit stream word; words
 // arrive in increasing w, each once.  Everything is written for predication
 // rather than branches: lanes of a warp code different blocks and would
 // otherwise diverge on every word boundary.
-CSW_HD uint32_t funnel_l(uint32_t lo, uint32_t hi, int s) {  // ((hi:lo) << s) >> 32, s in 0..31
+CSW_HD uint32_t funnel_l(uint32_t lo, uint32_t hi, int s) {  // ((hi:lo) << s) >> 32, s taken mod 32
 #if defined(__CUDA_ARCH__)
   return __funnelshift_l(lo, hi, s);
 #else
   return (uint32_t)(((((uint64_t)hi << 32) | lo) << (s & 31)) >> 32);
 #endif
 }
-CSW_HD uint32_t funnel_r(uint32_t lo, uint32_t hi, int s) {  // low word of (hi:lo) >> s, s in 0..31
+CSW_HD uint32_t funnel_r(uint32_t lo, uint32_t hi, int s) {  // low word of (hi:lo) >> s, s taken mod 32
 #if defined(__CUDA_ARCH__)
   return __funnelshift_r(lo, hi, s);
 #else
@@ -767,12 +772,12 @@ CSW_HD uint64_t decode_plane(Reader<WordSource>& rd, int& n, int& bits, const ui
     int L = lim < 8 ? lim : 8;
     L = bits < L ? bits : L;
     uint32_t e = dec_lut[dec_lut_index(L, st, rd.peek() & 0xffu)];
-    int used = (int)(e & 0xfu);
-    x |= (uint64_t)((e >> 8) & 0xffu) << n;
-    n += (int)((e >> 4) & 0xfu);
+    int used = dec_lut_used(e);
+    x |= (uint64_t)dec_lut_pattern(e) << n;
+    n += dec_lut_advance(e);
     bits -= used;
     rd.skip(used);
-    st = (int)(e >> 16);
+    st = dec_lut_state(e);
     if (st == 2) break;
   }
   return x;
@@ -827,13 +832,30 @@ CSW_HD void decode_block(WordSource& src, int maxbits, float (&f)[1 << (2 * DIMS
 template <class WordSrc>
 CSW_HD uint32_t peek_at(const WordSrc& src, int pos) {
   const int w = pos >> 5;
-  return funnel_r(src.word(w), src.word(w + 1), pos & 31);
+  return funnel_r(src.word(w), src.word(w + 1), pos);  // the shift uses pos mod 32
 }
-CSW_HD void or_at(uint32_t& xl, uint32_t& xh, uint32_t pat, int n) {  // x |= pat << n, n in 0..63
-  const int s = n & 31;
-  const uint32_t a = pat << s, b = funnel_l(pat, 0u, s);
-  xl |= n < 32 ? a : 0u;
-  xh |= n < 32 ? b : a;
+// low min(max(n, 0), 32) bits set, for any n
+CSW_HD uint32_t low_mask_sat(int n) {
+  const int k = n > 0 ? n : 0;
+#if defined(__CUDA_ARCH__)
+  uint32_t m;
+  asm("bmsk.clamp.b32 %0, 0, %1;" : "=r"(m) : "r"(k));
+  return m;
+#else
+  return k >= 32 ? 0xffffffffu : ((1u << k) - 1u);
+#endif
+}
+// (h:l) rotated right by r, r in 0..31
+CSW_HD void ror64_small(uint32_t& l, uint32_t& h, int r) {
+  const uint32_t t = funnel_r(l, h, r);
+  h = funnel_r(h, l, r);
+  l = t;
+}
+// (h:l) rotated left by r, r in 0..63
+CSW_HD void rol64(uint32_t& l, uint32_t& h, int r) {
+  const uint32_t a = (r & 32) ? h : l, b = (r & 32) ? l : h;  // halves after a rotation by 32
+  l = funnel_l(b, a, r);
+  h = funnel_l(a, b, r);
 }
 
 template <class WordSrc>
@@ -858,31 +880,45 @@ CSW_HD void decode_block3_pos(const WordSrc& src, int maxbits, float (&f)[64], c
         // first min(n, budget) bits verbatim (decode.cuh:143-145)
         const int left0 = maxbits - pos;
         const int m = n < left0 ? n : left0;
-        const int w = pos >> 5, s = pos & 31;
+        const int w = pos >> 5;
         const uint32_t w0 = src.word(w), w1 = src.word(w + 1), w2 = src.word(w + 2);
-        xl = funnel_r(w0, w1, s) & low_mask32(m < 32 ? m : 32);
-        xh = funnel_r(w1, w2, s) & low_mask32(m > 32 ? m - 32 : 0);
+        xl = funnel_r(w0, w1, pos) & low_mask_sat(m);
+        xh = funnel_r(w1, w2, pos) & low_mask_sat(m - 32);
         pos += m;
-        // group tests and unary runs (decode.cuh:147-164), up to eight stream bits per step
+        // group tests and unary runs (decode.cuh:147-164), up to eight stream
+        // bits per step.  The bits found are gathered in (ah:al), kept rotated
+        // so that position n is bit 0: a step ORs its pattern in at the bottom
+        // and rotates by the positions it advanced.
+        uint32_t al = 0u, ah = 0u;
         int st = 0;
         for (;;) {
+          // stream bits this step may read: up to eight, no further than the
+          // last open position (a run's final one is implied, so it stops one
+          // short) and no further than the block's budget
           const int left = maxbits - pos;
-          if (st == 1 && (n == 63 || left == 0)) {  // run cut short: the one is implied
-            or_at(xl, xh, 1u, n);
-            n++;
-            st = 0;
-          }
-          if (st == 0 && (n >= 64 || left == 0)) break;
-          const int lim = (st == 0 ? 64 : 63) - n;
+          const int lim = 64 - st - n;
           int L = lim < 8 ? lim : 8;
           L = left < L ? left : L;
+          if (L <= 0) {
+            if (st == 1) {  // run cut short: the one is implied
+              al |= 1u;
+              ror64_small(al, ah, 1);
+              n++;
+            }
+            break;
+          }
           const uint32_t en = dec_lut[dec_lut_index(L, st, peek_at(src, pos) & 0xffu)];
-          or_at(xl, xh, (en >> 8) & 0xffu, n);
-          n += (int)((en >> 4) & 0xfu);
-          pos += (int)(en & 0xfu);
-          st = (int)(en >> 16);
+          const int dn = dec_lut_advance(en);
+          al |= dec_lut_pattern(en);
+          ror64_small(al, ah, dn);
+          n += dn;
+          pos += dec_lut_used(en);
+          st = dec_lut_state(en);
           if (st == 2) break;
         }
+        rol64(al, ah, n);  // position 0 back to bit 0
+        xl |= al;
+        xh |= ah;
       }
       lo[k] = xl;
       hi[k] = xh;

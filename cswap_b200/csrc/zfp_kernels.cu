@@ -5,8 +5,8 @@
 // decode1/2.cuh).  Two families:
 //
 //  * slab kernels for the swap path's view (nx = ny = 32, contiguous, whole
-//    32-bit words per block): one CTA per group of 16 z-slabs (64 KiB, 256
-//    blocks), lane = zfp block held in registers.  A lane moves its block with
+//    32-bit words per block): one CTA per group of 8 z-slabs (32 KiB, 128
+//    blocks), four CTAs per SM, lane = zfp block held in registers.  A lane moves its block with
 //    sixteen 128-bit accesses (eight neighbouring lanes cover one 128-byte row
 //    segment, so a warp access touches four whole lines); stream words sit
 //    word-major in shared memory (bank = lane, so diverged lanes never
@@ -31,11 +31,12 @@ namespace csw {
 
 namespace {
 
-constexpr int kThreads = 256;                  // blocks per CTA iteration
+constexpr int kThreads = 128;                  // zfp blocks (lanes) per CTA
 constexpr int kSlabFloats = 1024;              // one 32x32 z-slab
-constexpr int kGroupSlabs = 16;                // z-slabs per CTA iteration
+constexpr int kGroupSlabs = kThreads / 16;      // z-slabs per CTA: kThreads / 64 tiles of four
+constexpr int kCtasPerSm = 512 / kThreads;      // by registers (128 per thread)
 
-// ---- word staging: word w of the block owned by thread t lives at [w * 256 + t] -----
+// ---- word staging: word w of the block owned by thread t lives at [w * kThreads + t] --
 // Staged stream words of the decoder: rows nwords and nwords + 1 are kept zero
 // so that reads just past a block need no bounds test.
 struct StageWords {
@@ -66,12 +67,12 @@ __device__ __forceinline__ int pad_src_z(int z, int vz) { return z < vz ? z : (z
 // =====================================================================================
 // slab encoder
 // =====================================================================================
-// One CTA per group of 16 z-slabs (256 blocks, lane = block).  A lane reads its
+// One CTA per group of 8 z-slabs (128 blocks, lane = block).  A lane reads its
 // 4x4x4 block with sixteen 128-bit loads (eight neighbouring lanes cover one
 // 128-byte row segment, so a warp load touches four full lines), codes it into
 // its own column of the word-major staging area and writes its own words out:
 // after the table is built no warp waits for another.
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 zfp_encode_slab_kernel(const float* __restrict__ in, uint32_t* __restrict__ out, uint32_t nz, int maxbits,
                        const PipeConsts kc) {
   extern __shared__ __align__(16) uint32_t smem_words[];
@@ -83,7 +84,7 @@ zfp_encode_slab_kernel(const float* __restrict__ in, uint32_t* __restrict__ out,
   const int tid = threadIdx.x;
   // my block: tile t of the group (4 slabs), block (bx, by) of its 8x8 grid
   const int t = tid >> 6, bx = tid & 7, by = (tid >> 3) & 7;
-  const uint32_t zt = (blockIdx.x * 4 + t) * 4;  // first slab of my tile
+  const uint32_t zt = (blockIdx.x * (kThreads / 64) + t) * 4;  // first slab of my tile
   const int vz = zt >= nz ? 0 : (nz - zt < 4 ? (int)(nz - zt) : 4);
   float f[64];
   if (vz > 0) {
@@ -101,7 +102,7 @@ zfp_encode_slab_kernel(const float* __restrict__ in, uint32_t* __restrict__ out,
       }
     }
   }
-  lut[tid] = enc_lut_entry((uint32_t)tid);
+  for (int i = tid; i < ENC_LUT_SIZE; i += kThreads) lut[i] = enc_lut_entry((uint32_t)i);
   for (int w = 0; w < nwords; w++) stage[w * kThreads + tid] = 0u;  // coded bits are OR-ed in
   __syncthreads();  // the table is complete
   if (vz == 0) return;
@@ -139,11 +140,11 @@ __device__ const DecTable g_dec_table = make_dec_table();
 static_assert(DEC_LUT_SIZE % (4 * kThreads) == 0, "table copy assumes whole 128-bit rounds");
 }  // namespace
 
-// One CTA per group of 16 z-slabs, lane = block, mirror image of the encoder: a
+// One CTA per group of 8 z-slabs, lane = block, mirror image of the encoder: a
 // lane pulls its own compressed words into its column of the word-major staging
 // area, parses them by bit position and stores the rebuilt 4x4x4 block with
 // sixteen 128-bit stores.  The only barrier is the one after the table copy.
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 zfp_decode_slab_kernel(const uint32_t* __restrict__ in, float* __restrict__ out, uint32_t nz, int maxbits) {
   extern __shared__ __align__(16) uint32_t smem_words[];
   const int nwords = maxbits >> 5;
@@ -152,7 +153,7 @@ zfp_decode_slab_kernel(const uint32_t* __restrict__ in, float* __restrict__ out,
 
   const int tid = threadIdx.x;
   const int t = tid >> 6, bx = tid & 7, by = (tid >> 3) & 7;
-  const uint32_t zt = (blockIdx.x * 4 + t) * 4;  // first slab of my tile
+  const uint32_t zt = (blockIdx.x * (kThreads / 64) + t) * 4;  // first slab of my tile
   uint32_t* col = stage + tid;
   if (zt < nz) {
     const uint32_t* src = in + ((size_t)blockIdx.x * kThreads + tid) * nwords;
