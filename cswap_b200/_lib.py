@@ -96,6 +96,7 @@ SIGNATURES = {
     "csw_sparse_layout_of": (_I, [_SZ, C.POINTER(SparseLayout)]),
     "csw_sparse_compress": (_I, [_P, _SZ, _P, _SZ, _P, _P]),
     "csw_sparse_compress_static": (_I, [_P, _SZ, _P, _SZ, _P, _P]),
+    "csw_sparse_compress_onepass": (_I, [_P, _SZ, _P, _SZ, _P, _P]),
     "csw_sparse_decompress": (_I, [_P, _SZ, _P, _P]),
     "csw_mgr_create": (_I, [C.POINTER(MgrConfig), C.POINTER(_P)]),
     "csw_mgr_destroy": (_I, [_P]),

@@ -106,8 +106,12 @@ def sparse_packed_bytes(n: int, nnz: int) -> int:
 
 
 def sparse_compress(t: torch.Tensor, out: Optional[torch.Tensor] = None,
-                    nnz_out: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """(packed uint8 buffer, one-element int32 device tensor holding nnz)."""
+                    nnz_out: Optional[torch.Tensor] = None, onepass: bool = False
+                    ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(packed uint8 buffer, one-element int32 device tensor holding nnz).
+
+    onepass=True reads the tensor once (csw_sparse_compress_onepass): same bitmap,
+    count and per-tile contents, tile segments in schedule order."""
     _require_cuda_f32(t, "t")
     n = t.numel()
     L = sparse_layout(n)
@@ -116,8 +120,9 @@ def sparse_compress(t: torch.Tensor, out: Optional[torch.Tensor] = None,
     if nnz_out is None:
         nnz_out = torch.zeros(1, dtype=torch.int32, device=t.device)
     with torch.cuda.device(t.device):
-        check(lib().csw_sparse_compress(t.data_ptr(), n, out.data_ptr(), out.numel(), nnz_out.data_ptr(),
-                                        _stream_ptr(t.device)), "csw_sparse_compress")
+        fn = lib().csw_sparse_compress_onepass if onepass else lib().csw_sparse_compress
+        check(fn(t.data_ptr(), n, out.data_ptr(), out.numel(), nnz_out.data_ptr(), _stream_ptr(t.device)),
+              "csw_sparse_compress")
     return out, nnz_out
 
 

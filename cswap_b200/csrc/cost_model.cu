@@ -127,7 +127,7 @@ csw_status csw_cost_fit(csw_mgr* m, csw_cost_model* model) {
       st = time_op(s, e0, e1, 5, [&] { return csw_zfp_decompress(d_c, zb, 32, 32, nz, mb, d_y, s); }, &t);
     t_zd.push_back(t);
     if (st == CSW_OK)
-      st = time_op(s, e0, e1, 5, [&] { return csw_sparse_compress(d_x, n, d_c, L.bound, d_nnz, s); }, &t);
+      st = time_op(s, e0, e1, 5, [&] { return csw_sparse_compress_onepass(d_x, n, d_c, L.bound, d_nnz, s); }, &t);
     t_se.push_back(t);
     if (st == CSW_OK) st = time_op(s, e0, e1, 5, [&] { return csw_sparse_decompress(d_c, n, d_y, s); }, &t);
     t_sd.push_back(t);

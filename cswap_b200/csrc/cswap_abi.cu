@@ -192,6 +192,26 @@ csw_status csw_sparse_compress(const float* d_in, size_t n, void* d_out, size_t 
   return e == cudaSuccess ? CSW_OK : cuda_fail(e);
 }
 
+csw_status csw_sparse_compress_onepass(const float* d_in, size_t n, void* d_out, size_t cap, uint32_t* nnz_out,
+                                       csw_stream_t stream) {
+  csw_sparse_layout L;
+  csw_status st = csw_sparse_layout_of(n, &L);
+  if (st != CSW_OK) return st;
+  if ((!d_in && n) || !d_out || !nnz_out) return CSW_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(d_out) & 15) != 0) return CSW_ERR_ARG;
+  if (cap < L.bound) return CSW_ERR_SIZE;
+  cudaPointerAttributes attr{};
+  if (cudaPointerGetAttributes(&attr, nnz_out) != cudaSuccess || attr.type != cudaMemoryTypeDevice) {
+    cudaGetLastError();
+    return CSW_ERR_ARG;  // the cursor is updated with device atomics
+  }
+  char* base = static_cast<char*>(d_out);
+  cudaError_t e = sparse_compress_onepass_launch(d_in, n, reinterpret_cast<uint32_t*>(base + L.bitmap),
+                                                 reinterpret_cast<float*>(base + L.values),
+                                                 reinterpret_cast<uint32_t*>(base + L.tile_off), nnz_out, stream);
+  return e == cudaSuccess ? CSW_OK : cuda_fail(e);
+}
+
 csw_status csw_sparse_decompress(const void* d_in, size_t n, float* d_out, csw_stream_t stream) {
   csw_sparse_layout L;
   csw_status st = csw_sparse_layout_of(n, &L);

@@ -13,6 +13,9 @@
 //                   round-trip exactly.
 //  count -> scan -> pack, three launches, no inter-CTA waiting; the total is
 //                   written to a caller-supplied word (device or mapped host).
+//  single pass    - same bitmap and per-tile contents from one read of the
+//                   tensor; tiles claim their segments with an atomic add, so
+//                   segment order follows the schedule, not the element order.
 //  legacy format  - the reference's `begin | bitmap | values` layout with its
 //                   P-worker chunking, one warp per worker, behind the
 //                   reference's own entry-point names.
@@ -178,6 +181,56 @@ sparse_pack_kernel(const uint32_t* __restrict__ in, uint64_t n, const uint32_t* 
   }
 }
 
+// ---- single pass: tiles claim their value segments from a cursor ---------------------
+// Reads the tensor once.  A tile counts its non-zeros, claims that many slots
+// with one atomic add on `cursor` (which must be zero at launch and holds the
+// total afterwards) and records where its segment starts in tile_off; bitmap
+// and per-tile contents are the same as the three-pass result, but segments
+// sit in the order the tiles claimed them, so the values array (not what
+// decompression returns) can differ from run to run.  No CTA waits for another.
+__global__ void __launch_bounds__(kThreads)
+sparse_onepass_kernel(const uint32_t* __restrict__ in, uint64_t n, uint32_t* __restrict__ bitmap,
+                      uint32_t* __restrict__ tile_off, uint32_t* __restrict__ values, uint32_t* __restrict__ cursor) {
+  __shared__ uint32_t warp_cnt[kThreads / 32];
+  __shared__ uint32_t tile_base;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint64_t base = (uint64_t)blockIdx.x * kTile + (uint64_t)warp * (kWordsPerWarp * 32);
+  uint32_t v[kWordsPerWarp], w[kWordsPerWarp];
+#pragma unroll
+  for (int j = 0; j < kWordsPerWarp; j++) {
+    const uint64_t i = base + j * 32 + lane;
+    v[j] = i < n ? __ldg(in + i) : 0u;
+  }
+  uint32_t mine = 0, cnt = 0;
+#pragma unroll
+  for (int j = 0; j < kWordsPerWarp; j++) {
+    w[j] = __ballot_sync(0xffffffffu, v[j] != 0u);
+    cnt += __popc(w[j]);
+    if (lane == j) mine = w[j];
+  }
+  const uint64_t word0 = base >> 5, nwords = (n + 31) >> 5;
+  if (lane < kWordsPerWarp && word0 + lane < nwords) bitmap[word0 + lane] = mine;
+  if (lane == 0) warp_cnt[warp] = cnt;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t total = 0;
+#pragma unroll
+    for (int i = 0; i < kThreads / 32; i++) total += warp_cnt[i];
+    const uint32_t at = atomicAdd(cursor, total);
+    tile_off[blockIdx.x] = at;
+    tile_base = at;
+  }
+  __syncthreads();
+  uint32_t off = tile_base;
+  for (int i = 0; i < warp; i++) off += warp_cnt[i];
+  const uint32_t lt = lanemask_lt();
+#pragma unroll
+  for (int j = 0; j < kWordsPerWarp; j++) {
+    if (v[j] != 0u) values[off + __popc(w[j] & lt)] = v[j];
+    off += __popc(w[j]);
+  }
+}
+
 // ---- decompression -----------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads)
 sparse_unpack_kernel(const uint32_t* __restrict__ bitmap, const uint32_t* __restrict__ values,
@@ -201,12 +254,22 @@ sparse_unpack_kernel(const uint32_t* __restrict__ bitmap, const uint32_t* __rest
   for (int i = 0; i < warp; i++) off += warp_cnt[i];
   const uint32_t my_off = off + x - c;
   const uint32_t lt = lanemask_lt();
+  // three separate sweeps so that all sixteen gathers of a thread are in flight
+  // together (the warp shuffles would otherwise pin each load to its store)
+  uint32_t src[kWordsPerWarp];  // index of my value, or ~0 when my element is zero
 #pragma unroll
   for (int j = 0; j < kWordsPerWarp; j++) {
     const uint32_t w = __shfl_sync(0xffffffffu, mine, j);
     const uint32_t o = __shfl_sync(0xffffffffu, my_off, j);
+    src[j] = ((w >> lane) & 1u) ? o + __popc(w & lt) : 0xffffffffu;
+  }
+  uint32_t val[kWordsPerWarp];
+#pragma unroll
+  for (int j = 0; j < kWordsPerWarp; j++) val[j] = src[j] != 0xffffffffu ? __ldg(values + src[j]) : 0u;
+#pragma unroll
+  for (int j = 0; j < kWordsPerWarp; j++) {
     const uint64_t i = base + j * 32 + lane;
-    if (i < n) out[i] = ((w >> lane) & 1u) ? __ldg(values + o + __popc(w & lt)) : 0u;
+    if (i < n) out[i] = val[j];
   }
 }
 
@@ -348,6 +411,16 @@ cudaError_t sparse_compress_scratch_launch(const float* in, uint64_t n, uint32_t
     sparse_pack_kernel<<<ntiles, kThreads, 0, stream>>>(reinterpret_cast<const uint32_t*>(in), n, tile_off,
                                                         reinterpret_cast<uint32_t*>(values));
   }
+  return cudaGetLastError();
+}
+
+cudaError_t sparse_compress_onepass_launch(const float* in, uint64_t n, uint32_t* bitmap, float* values,
+                                           uint32_t* tile_off, uint32_t* nnz_out, cudaStream_t stream) {
+  const uint32_t ntiles = (uint32_t)((n + kTile - 1) / kTile);
+  cudaError_t e = cudaMemsetAsync(nnz_out, 0, sizeof(uint32_t), stream);  // the cursor, then the total
+  if (e != cudaSuccess || !ntiles) return e;
+  sparse_onepass_kernel<<<ntiles, kThreads, 0, stream>>>(reinterpret_cast<const uint32_t*>(in), n, bitmap, tile_off,
+                                                         reinterpret_cast<uint32_t*>(values), nnz_out);
   return cudaGetLastError();
 }
 

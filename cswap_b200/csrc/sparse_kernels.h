@@ -18,6 +18,12 @@ cudaError_t sparse_compress_launch(const float* in, uint64_t n, uint32_t* bitmap
 cudaError_t sparse_compress_scratch_launch(const float* in, uint64_t n, uint32_t* bitmap, float* values,
                                            uint32_t* tile_off, uint32_t* tile_cnt_scratch, uint32_t* nnz_out,
                                            cudaStream_t stream);
+// Single pass over the tensor: same bitmap, same per-tile contents, but the
+// tiles' value segments are laid out in the order the tiles claimed them
+// (tile_off says where each one starts).  *nnz_out must be DEVICE memory: it is
+// the allocation cursor during the kernel and holds the total afterwards.
+cudaError_t sparse_compress_onepass_launch(const float* in, uint64_t n, uint32_t* bitmap, float* values,
+                                           uint32_t* tile_off, uint32_t* nnz_out, cudaStream_t stream);
 cudaError_t sparse_decompress_launch(const uint32_t* bitmap, const float* values, const uint32_t* tile_off, uint64_t n,
                                      float* out, cudaStream_t stream);
 

@@ -423,7 +423,7 @@ csw_status csw_swap_out(csw_mgr* m, const float* d_ptr, size_t numel, int policy
     m->free_slots.pop_back();
     t->nnz_host = m->nnz_slots + t->nnz_slot;
     uint32_t* nnz_dev = m->nnz_dev + t->nnz_slot;
-    st = csw_sparse_compress(d_ptr, numel, t->stage, t->stage_cap, nnz_dev, m->s_codec);
+    st = csw_sparse_compress_onepass(d_ptr, numel, t->stage, t->stage_cap, nnz_dev, m->s_codec);
     if (st == CSW_OK) {
       e = cudaEventRecord(t->ev_read, m->s_codec);
       if (e == cudaSuccess) e = cudaStreamWaitEvent(m->s_d2h, t->ev_read, 0);

@@ -37,6 +37,85 @@ def _check_native(cs, O, a):
     return nnz
 
 
+def _check_onepass(cs, O, a):
+    """Single-pass compressor: the bitmap and the count are the oracle's, every
+    tile's segment holds the oracle's values for that tile, the segments tile
+    the values array without gaps or overlaps (in whatever order), and both the
+    library and the oracle decode the buffer back to the input."""
+    import torch
+    n = a.size
+    t = torch.from_numpy(a).cuda()
+    packed, nnz_t = cs.sparse_compress(t, onepass=True)
+    nnz = int(nnz_t.item())
+    bitmap, values, tile_off, ref_nnz = O.sparse_compress(a)
+    assert nnz == ref_nnz
+    L = cs.sparse_layout(n)
+    buf = packed.cpu().numpy()
+    tiles = (n + 4095) // 4096
+    words = (n + 31) // 32
+    got_bitmap = buf[L.bitmap:L.bitmap + 4 * words].view(np.uint32)
+    assert np.array_equal(got_bitmap, bitmap)
+    got_off = buf[L.tile_off:L.tile_off + 4 * tiles].view(np.uint32).astype(np.int64)
+    got_vals = buf[L.values:L.values + 4 * nnz].view(np.uint32)
+    ref_off = np.append(tile_off.astype(np.int64), ref_nnz)
+    cnt = np.diff(ref_off)
+    order = np.argsort(got_off, kind="stable")
+    nonempty = order[cnt[order] > 0]
+    # segments of the non-empty tiles are disjoint and cover [0, nnz)
+    starts = got_off[nonempty]
+    assert np.array_equal(starts, np.concatenate(([0], np.cumsum(cnt[nonempty])[:-1]))) if nonempty.size else nnz == 0
+    assert np.all(got_off <= nnz)
+    ref_vals = values.view(np.uint32)
+    for tl in range(tiles):
+        assert np.array_equal(got_vals[got_off[tl]:got_off[tl] + cnt[tl]], ref_vals[ref_off[tl]:ref_off[tl + 1]])
+    out = cs.sparse_decompress(packed, n)
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), a.view(np.uint32))
+    # the oracle's tile-by-tile decoder reads the same buffer
+    dec = np.zeros(n, dtype=np.uint32)
+    for tl in range(tiles):
+        lo, hi = tl * 4096, min(n, (tl + 1) * 4096)
+        bits = np.unpackbits(got_bitmap[lo // 32:(hi + 31) // 32].view(np.uint8), bitorder="little")[:hi - lo]
+        dec[lo:hi][bits.astype(bool)] = got_vals[got_off[tl]:got_off[tl] + cnt[tl]]
+    assert np.array_equal(dec, a.view(np.uint32))
+    return nnz
+
+
+@pytest.mark.parametrize("n", [1, 33, 4095, 4096, 4097, 8192 + 17, (1 << 20) + 5, 128 * 128 * 16 * 16])
+def test_onepass_matches_oracle_per_tile(cs, oracle, n):
+    _check_onepass(cs, oracle, util.relu_normal(n, 0.75, seed=n + 1))
+
+
+def test_onepass_special_patterns(cs, oracle):
+    n = 5 * 4096 + 100
+    _check_onepass(cs, oracle, np.zeros(n, dtype=np.float32))
+    _check_onepass(cs, oracle, util.normal(n, 1) + np.float32(10))
+    a = util.relu_normal(n, 0.5, 3)
+    a[::7] = -0.0
+    a[5::11] = np.nan
+    a.view(np.uint32)[9::17] = 0x7fc12345
+    _check_onepass(cs, oracle, a)
+
+
+def test_onepass_full_size_and_host_count_rejected(cs):
+    """256 MiB: count and round trip; a count word outside device memory is refused."""
+    import torch
+    n = 64 * 1024 * 1024
+    g = torch.Generator(device="cuda").manual_seed(6)
+    t = torch.relu(torch.randn(n, device="cuda", generator=g))
+    packed, nnz_t = cs.sparse_compress(t, onepass=True)
+    assert int(nnz_t.item()) == int(torch.count_nonzero(t).item())
+    out = cs.sparse_decompress(packed, n)
+    assert torch.equal(out.view(torch.int32), t.view(torch.int32))
+    # the multiset of packed values is that of the non-zeros
+    L = cs.sparse_layout(n)
+    vals = packed[L.values:L.values + 4 * int(nnz_t.item())].view(torch.float32)
+    assert torch.equal(torch.sort(vals).values, torch.sort(t[t != 0]).values)
+    host_word = torch.zeros(1, dtype=torch.int32).pin_memory()
+    st = cs.lib().csw_sparse_compress_onepass(t.data_ptr(), n, packed.data_ptr(), packed.numel(),
+                                              host_word.data_ptr(), None)
+    assert st == 1  # CSW_ERR_ARG
+
+
 @pytest.mark.parametrize("zf", [0.5, 0.75, 0.9])
 def test_config2_relu_activations(cs, oracle, zf, capsys):
     # float32 [128,128,16,16] = 16 MiB
