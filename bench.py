@@ -264,6 +264,11 @@ def run_model_workload(args):
     if args.workload == "vgg16":
         results["reference_split_zfp8"] = W.timed_steps(model, fresh(W.vgg16_reference_policy), make_batch, steps,
                                                         warmup)
+        # the baseline planners of the reference's drivers (policy_ 3 and 4)
+        results["vdnn_baseline"] = W.timed_steps(model, fresh(lambda e: W.vgg16_baseline_policy(e, 3)), make_batch,
+                                                 steps, warmup)
+        results["superneurons_baseline"] = W.timed_steps(model, fresh(lambda e: W.vgg16_baseline_policy(e, 4)),
+                                                         make_batch, steps, warmup)
     # self-tuning: profile one step, fit the cost model on this GPU, decide per tensor
     exe = fresh(lambda e: None)
     exe.profile = True
@@ -295,8 +300,10 @@ def run_model_workload(args):
                        "policy_counts_lossy_everywhere": counts_all},
             "step_ms": {"no_swap": t_none, "raw_swap": t_raw, "self_tuned": t_tuned,
                         "self_tuned_lossy_everywhere": results["self_tuned_lossy_everywhere"]["ms_per_step"],
-                        **({"reference_split_zfp8": results["reference_split_zfp8"]["ms_per_step"]}
-                           if "reference_split_zfp8" in results else {})},
+                        **{k: results[k]["ms_per_step"]
+                           for k in ("reference_split_zfp8", "vdnn_baseline", "superneurons_baseline")
+                           if k in results}},
+            "peak_device_mib": {k: round(v["peak_device_bytes"] / 2**20, 1) for k, v in results.items()},
             "raw_swap": raw, "self_tuned": tuned,
             "activation_bytes_per_link_byte": {
                 "raw_swap": raw["activation_bytes_per_step"] / max(raw["link_bytes_out_per_step"], 1),

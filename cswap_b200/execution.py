@@ -3,8 +3,8 @@
 `Execution` keeps the interface the CSWAP+ model drivers use
 (CSWAP+/Execution.h:38-447): `init_`, `preforward`, `pre`, `post`,
 `postforward`, the public tables `policy`, `begin_stage`, `index`, `policy_`,
-and the policy codes 0 keep / 2 raw / 3 sparse / 6 ZFP.  A driver wraps every
-layer as
+and the policy codes 0 keep / 1 drop and recompute / 2 raw / 3 sparse / 6 ZFP.
+A driver wraps every layer as
 
     exe.pre(x)            # may start swapping x out (Execution.h:65-133)
     y = layer(x)
@@ -12,6 +12,16 @@ layer as
                           # (Execution.h:217-310)
 
 and brackets the forward pass with `preforward()` / `postforward()`.
+
+Policy 1 (Execution.h:243-247 clears the storage and leaves the rebuilding to
+the modified engine, which is not part of the reference tree): `post` takes
+the layer as an extra argument, `post(x, y, type, isomit, forward=layer)`, and a
+dropped tensor is rebuilt in backward by running its producer again on the
+producer's own input, which is in turn swapped in or rebuilt as needed.  Only
+stateless callables may be passed (a BatchNorm module would update its running
+statistics a second time; pass a closure over F.batch_norm without them).  A
+tensor whose producer was not given stays on the device.  `policy_` 3 and 4
+select the vDNN and SuperNeurons baselines as in Execution.h:70,243,248.
 
 The reference swaps the storage's DataPtr under the autograd graph and relies
 on a modified engine to bring it back.  On stock PyTorch the same effect is
@@ -49,7 +59,7 @@ class _Record:
     """Residency of one activation storage: on the device (`tensor`) or
     swapped out (`ticket`)."""
 
-    __slots__ = ("tensor", "ticket", "numel", "order", "exe", "__weakref__")
+    __slots__ = ("tensor", "ticket", "numel", "order", "exe", "producer", "dropped", "__weakref__")
 
     def __init__(self, tensor: torch.Tensor, exe: "Execution"):
         self.tensor: Optional[torch.Tensor] = tensor
@@ -57,12 +67,23 @@ class _Record:
         self.numel = tensor.numel()
         self.order = -1
         self.exe = weakref.ref(exe)
+        self.producer = None   # (callable, packed inputs) when the driver passed the layer to post()
+        self.dropped = False   # policy 1: let go without a copy, rebuilt by `producer`
 
     def materialize(self) -> torch.Tensor:
         if self.tensor is None:
             exe = self.exe()
-            self.tensor = exe.mgr.swap_in(self.ticket).view(-1)
-            exe._after_swap_in(self)
+            if self.ticket is not None:
+                self.tensor = exe.mgr.swap_in(self.ticket).view(-1)
+                exe._after_swap_in(self)
+            else:
+                fn, packed = self.producer
+                with torch.no_grad():
+                    out = fn(*[exe._unpack(p) for p in packed])
+                if out.numel() != self.numel or out.dtype != torch.float32:
+                    raise RuntimeError("recomputed activation does not match the dropped one")
+                self.tensor = out.detach().contiguous().view(-1)
+                exe.recomputed_tensors += 1
         return self.tensor
 
     def __del__(self):
@@ -97,10 +118,13 @@ class Execution:
         self._records: "weakref.WeakValueDictionary[int, _Record]" = weakref.WeakValueDictionary()
         self._pending: List[_Record] = []
         self._swapped: List["weakref.ref[_Record]"] = []
+        self._produced: List[_Record] = []  # keeps producer notes alive until autograd holds the records
         self._hooks = None
         self._prof: Dict[int, dict] = {}
         self._prof_start = None
         self.swapped_tensors = 0
+        self.dropped_tensors = 0
+        self.recomputed_tensors = 0
         self.skipped_for_memory = 0
 
     # ---- set-up (Execution.h:46-64) -------------------------------------------
@@ -121,6 +145,7 @@ class Execution:
         self.index = -1
         self._pending.clear()
         self._swapped.clear()
+        self._produced.clear()
         if self._hooks is None:
             self._hooks = torch.autograd.graph.saved_tensors_hooks(self._pack, self._unpack)
             self._hooks.__enter__()
@@ -130,6 +155,7 @@ class Execution:
             self._hooks.__exit__(None, None, None)
             self._hooks = None
         self._pending.clear()
+        self._produced.clear()
 
     # ---- saved-tensor hooks ------------------------------------------------------
     def _eligible(self, t: torch.Tensor) -> bool:
@@ -167,8 +193,10 @@ class Execution:
     # ---- pre / post ----------------------------------------------------------------
     def _effective_policy(self, tid: int, layer_type: LayerType) -> int:
         pol = self.policy[tid] if tid < len(self.policy) else POLICY_KEEP
+        if pol == POLICY_DROP or (self.policy_ == 4 and layer_type != LayerType.CONV):
+            return POLICY_DROP  # Execution.h:243: SuperNeurons rebuilds the inputs of non-conv layers
         if layer_type == LayerType.CONV and self.policy_ > 2:
-            return POLICY_RAW  # vDNN / SuperNeurons baselines (Execution.h:70)
+            return POLICY_RAW  # vDNN / SuperNeurons baselines (Execution.h:70,248)
         return pol
 
     def pre(self, x: TensorOrList, layer_type: LayerType = LayerType.ACT) -> None:
@@ -179,10 +207,16 @@ class Execution:
             if tid < 0 or tid >= len(self.begin_stage) or self.index != self.begin_stage[tid] or t.grad_fn is None:
                 continue
             pol = self._effective_policy(tid, layer_type)
-            if pol not in (POLICY_RAW, POLICY_SPARSE, POLICY_ZFP) or not self._eligible(t):
+            if pol not in (POLICY_DROP, POLICY_RAW, POLICY_SPARSE, POLICY_ZFP) or not self._eligible(t):
                 continue
             rec = self._record_for(t)
-            if rec.ticket is not None:
+            if rec.ticket is not None or rec.dropped:
+                continue
+            if pol == POLICY_DROP:
+                if rec.producer is not None:  # without its producer the tensor simply stays
+                    rec.dropped = True
+                    self._pending.append(rec)
+                    self.dropped_tensors += 1
                 continue
             try:
                 rec.ticket = self.mgr.swap_out(rec.tensor, pol)
@@ -201,9 +235,16 @@ class Execution:
             self._prof_start = ev
 
     def post(self, x: TensorOrList, y: torch.Tensor, layer_type: LayerType = LayerType.ACT,
-             isomit: bool = False) -> None:
+             isomit: bool = False, forward=None) -> None:
         y.tensor_id = self.index
         inputs = [x] if isinstance(x, torch.Tensor) else list(x)
+        if forward is not None and self._hooks is not None and self._eligible(y) and not any(
+                t.is_cuda and t.untyped_storage().data_ptr() == y.untyped_storage().data_ptr() for t in inputs):
+            # how to rebuild y should it be dropped: its producer and the producer's inputs
+            # (a view of an input shares the input's record and is rebuilt with it)
+            rec = self._record_for(y)
+            rec.producer = (forward, [self._pack(t) for t in inputs])
+            self._produced.append(rec)
         if self.profile:
             ev = torch.cuda.Event(enable_timing=True)
             ev.record()

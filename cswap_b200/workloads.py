@@ -60,7 +60,7 @@ class VGG16(nn.Module):
         for layer, lt in zip(self.features, self.types):
             exe.pre(pre, lt)
             out = layer(pre)
-            exe.post(pre, out, lt)
+            exe.post(pre, out, lt, False, _stateless(layer))
             pre = out
         exe.pre(pre)
         out = pre.view(pre.size(0), -1)
@@ -75,6 +75,27 @@ class VGG16(nn.Module):
         exe.post([pre, target], loss, LayerType.ACT, True)
         exe.postforward()
         return loss
+
+
+def _stateless(layer: nn.Module):
+    """The layer as a function that can be run a second time in backward to
+    rebuild a dropped output: BatchNorm without its running statistics (the
+    training-mode output does not depend on them), everything else as is."""
+    if isinstance(layer, nn.BatchNorm2d):
+        return lambda t, m=layer: F.batch_norm(t, None, None, m.weight, m.bias, True, 0.0, m.eps)
+    return layer
+
+
+def vgg16_baseline_policy(exe: Execution, planner: int) -> None:
+    """The baseline planners as the reference's drivers set them up
+    (Desnet-cifar10.cpp:732-745): an all-zero policy table with `policy_` 3 (vDNN:
+    raw swap of every conv input) or 4 (SuperNeurons: the same, and the inputs
+    of all other layers dropped and rebuilt)."""
+    n = len(exe.policy)
+    for i in range(min(50, n)):
+        exe.begin_stage[i] = i + 1
+        exe.policy[i] = POLICY_KEEP
+    exe.policy_ = planner
 
 
 def vgg16_reference_policy(exe: Execution, compressed: int = POLICY_ZFP) -> None:
@@ -168,6 +189,7 @@ def timed_steps(model: nn.Module, exe: Execution, make_batch: Callable[[], Tuple
         if it == warmup:
             torch.cuda.synchronize()
             exe.mgr.reset_stats()
+            torch.cuda.reset_peak_memory_stats()
         hx, hy = make_batch()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -191,4 +213,7 @@ def timed_steps(model: nn.Module, exe: Execution, make_batch: Callable[[], Tuple
     return {"ms_per_step": sum(times) / n, "ms_median": times[len(times) // 2], "loss": loss_val,
             "swapped_tensors_per_step": s["swap_outs"] / n, "activation_bytes_per_step": s["raw_bytes_out"] / n,
             "link_bytes_out_per_step": s["moved_bytes_out"] / n, "link_bytes_in_per_step": s["moved_bytes_in"] / n,
-            "pinned_high_water": s["pinned_high_water"], "staging_high_water": s["staging_high_water"]}
+            "pinned_high_water": s["pinned_high_water"], "staging_high_water": s["staging_high_water"],
+            "peak_device_bytes": torch.cuda.max_memory_allocated(),
+            "dropped_tensors_per_step": exe.dropped_tensors / max(warmup + steps, 1),
+            "recomputed_tensors_per_step": exe.recomputed_tensors / max(warmup + steps, 1)}

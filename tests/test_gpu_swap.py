@@ -151,11 +151,12 @@ def _small_net(torch):
     return nn.Sequential(*layers).cuda()
 
 
-def _step(cs, torch, net, x, y, policy_for):
+def _step(cs, torch, net, x, y, policy_for, planner=1, give_producers=False):
     """One forward/backward with every layer wrapped in pre/post; returns loss and grads."""
     exe = cs.Execution()
     n = len(net)
     exe.init_(n + 1)
+    exe.policy_ = planner
     for i in range(n):
         exe.begin_stage[i] = i + 1
         exe.policy[i] = policy_for(i, net[i])
@@ -167,7 +168,7 @@ def _step(cs, torch, net, x, y, policy_for):
         lt = cs.LayerType.CONV if isinstance(layer, torch.nn.Conv2d) else cs.LayerType.ACT
         exe.pre(h, lt)
         out = layer(h)
-        exe.post(h, out, lt)
+        exe.post(h, out, lt, False, layer if give_producers else None)
         h = out
     exe.postforward()
     loss = torch.nn.functional.cross_entropy(h, y)
@@ -196,6 +197,56 @@ def test_execution_lossless_policies_do_not_change_training(cs):
     _, _, s_raw, _ = _step(cs, torch, net, x, y, lambda i, l: cs.POLICY_RAW if isinstance(l, torch.nn.ReLU) else 0)
     _, _, s_sp, _ = _step(cs, torch, net, x, y, lambda i, l: cs.POLICY_SPARSE if isinstance(l, torch.nn.ReLU) else 0)
     assert s_sp["moved_bytes_out"] < 0.8 * s_raw["moved_bytes_out"]
+
+
+def test_execution_drop_and_recompute(cs):
+    """Policy 1 (Execution.h:243-247): the tensor is let go without a copy and
+    rebuilt in backward from its producer; training is unchanged bit for bit.
+    Chains of dropped tensors rebuild each other; without a producer the
+    tensor stays."""
+    import torch
+    net = _small_net(torch)
+    x = torch.randn(64, 3, 32, 32, device="cuda")
+    y = torch.randint(0, 10, (64,), device="cuda")
+    torch.backends.cudnn.deterministic = True
+    base_loss, base_grads, _, _ = _step(cs, torch, net, x, y, lambda i, l: cs.POLICY_KEEP)
+    # every wrapped tensor dropped: each rebuild pulls in the one before it
+    loss, grads, stats, exe = _step(cs, torch, net, x, y, lambda i, l: cs.POLICY_DROP, give_producers=True)
+    assert exe.dropped_tensors >= 6 and exe.recomputed_tensors >= 4 and stats["swap_outs"] == 0
+    assert loss == base_loss
+    for g, b in zip(grads, base_grads):
+        assert torch.equal(g, b)
+    # mixed: ReLU outputs dropped, the rest swapped raw, so rebuilding a ReLU output swaps its input in
+    loss, grads, stats, exe = _step(cs, torch, net, x, y,
+                                    lambda i, l: cs.POLICY_DROP if isinstance(l, torch.nn.ReLU) else cs.POLICY_RAW,
+                                    give_producers=True)
+    assert exe.dropped_tensors >= 3 and exe.recomputed_tensors >= 2 and stats["swap_ins"] >= 2
+    assert loss == base_loss
+    for g, b in zip(grads, base_grads):
+        assert torch.equal(g, b)
+    # no producer given: policy 1 leaves the tensors where they are
+    loss, grads, stats, exe = _step(cs, torch, net, x, y, lambda i, l: cs.POLICY_DROP)
+    assert exe.dropped_tensors == 0 and exe.recomputed_tensors == 0 and loss == base_loss
+
+
+def test_execution_baseline_planners(cs):
+    """policy_ 3 (vDNN) swaps exactly the inputs of conv layers raw; policy_ 4
+    (SuperNeurons) also drops and rebuilds the inputs of the other layers
+    (Execution.h:70,243,248).  Both leave training unchanged."""
+    import torch
+    net = _small_net(torch)
+    n_conv = sum(isinstance(l, torch.nn.Conv2d) for l in net)
+    x = torch.randn(64, 3, 32, 32, device="cuda")
+    y = torch.randint(0, 10, (64,), device="cuda")
+    torch.backends.cudnn.deterministic = True
+    base_loss, base_grads, _, _ = _step(cs, torch, net, x, y, lambda i, l: cs.POLICY_KEEP)
+    loss, grads, stats, exe = _step(cs, torch, net, x, y, lambda i, l: cs.POLICY_KEEP, planner=3, give_producers=True)
+    # the first conv reads the network input, which no layer produced: nothing to swap there
+    assert stats["swap_outs"] == n_conv - 1 and exe.dropped_tensors == 0
+    assert loss == base_loss and all(torch.equal(g, b) for g, b in zip(grads, base_grads))
+    loss, grads, stats, exe = _step(cs, torch, net, x, y, lambda i, l: cs.POLICY_KEEP, planner=4, give_producers=True)
+    assert stats["swap_outs"] == n_conv - 1 and exe.dropped_tensors >= 2 and exe.recomputed_tensors >= 1
+    assert loss == base_loss and all(torch.equal(g, b) for g, b in zip(grads, base_grads))
 
 
 def test_execution_zfp_equals_codec_applied_to_activations(cs):
