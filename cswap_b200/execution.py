@@ -59,7 +59,7 @@ class _Record:
     """Residency of one activation storage: on the device (`tensor`) or
     swapped out (`ticket`)."""
 
-    __slots__ = ("tensor", "ticket", "numel", "order", "exe", "producer", "dropped", "__weakref__")
+    __slots__ = ("tensor", "ticket", "numel", "order", "exe", "producer", "dropped", "saved", "__weakref__")
 
     def __init__(self, tensor: torch.Tensor, exe: "Execution"):
         self.tensor: Optional[torch.Tensor] = tensor
@@ -69,12 +69,19 @@ class _Record:
         self.exe = weakref.ref(exe)
         self.producer = None   # (callable, packed inputs) when the driver passed the layer to post()
         self.dropped = False   # policy 1: let go without a copy, rebuilt by `producer`
+        self.saved = False     # autograd holds it for backward (a pack hook has seen it)
 
     def materialize(self) -> torch.Tensor:
         if self.tensor is None:
             exe = self.exe()
             if self.ticket is not None:
-                self.tensor = exe.mgr.swap_in(self.ticket).view(-1)
+                back = exe.mgr.reclaim(self.ticket)
+                if back is not None:
+                    # needed again before it had left the device: take it back as it is
+                    self.tensor = back.view(-1)
+                    self.ticket = None
+                else:
+                    self.tensor = exe.mgr.swap_in(self.ticket).view(-1)
                 exe._after_swap_in(self)
             else:
                 fn, packed = self.producer
@@ -119,8 +126,11 @@ class Execution:
         self._pending: List[_Record] = []
         self._swapped: List["weakref.ref[_Record]"] = []
         self._produced: List[_Record] = []  # keeps producer notes alive until autograd holds the records
+        self._deferred: List[tuple] = []    # (record, policy): swap only if the running layer saves the tensor
+        self.skipped_unsaved = 0
         self._hooks = None
         self._prof: Dict[int, dict] = {}
+        self._prof_saved: Dict[int, bool] = {}
         self._prof_start = None
         self.swapped_tensors = 0
         self.dropped_tensors = 0
@@ -146,6 +156,7 @@ class Execution:
         self._pending.clear()
         self._swapped.clear()
         self._produced.clear()
+        self._deferred.clear()
         if self._hooks is None:
             self._hooks = torch.autograd.graph.saved_tensors_hooks(self._pack, self._unpack)
             self._hooks.__enter__()
@@ -175,6 +186,15 @@ class Execution:
     def _pack(self, t: torch.Tensor):
         if not self._eligible(t):
             return t
+        rec = self._record_for(t)
+        rec.saved = True
+        return _Packed(rec, t.shape, t.stride(), t.storage_offset())
+
+    def _ref(self, t: torch.Tensor):
+        """Like _pack, for the producer notes: a way back to the tensor that does
+        not count as autograd having saved it."""
+        if not self._eligible(t):
+            return t
         return _Packed(self._record_for(t), t.shape, t.stride(), t.storage_offset())
 
     def _unpack(self, p):
@@ -187,7 +207,9 @@ class Execution:
         for i in range(rec.order - 1, -1, -1):
             r = self._swapped[i]() if i < len(self._swapped) else None
             if r is not None and r.tensor is None and r.ticket is not None:
-                self.mgr.prefetch(r.ticket)
+                # a lossless ticket still on its way out may yet be taken back whole
+                if r.ticket.policy == POLICY_ZFP or self.mgr.out_done(r.ticket):
+                    self.mgr.prefetch(r.ticket)
                 break
 
     # ---- pre / post ----------------------------------------------------------------
@@ -218,21 +240,30 @@ class Execution:
                     self._pending.append(rec)
                     self.dropped_tensors += 1
                 continue
-            try:
-                rec.ticket = self.mgr.swap_out(rec.tensor, pol)
-            except CswapError as err:
-                if err.status != 4:  # pools exhausted: this tensor simply stays on the device
-                    raise
-                self.skipped_for_memory += 1
+            if not rec.saved:
+                # Nothing has saved this tensor for backward yet.  Only the layer about to
+                # run still can (this is its last forward use): copy it out afterwards if it
+                # did, and not at all if it did not - it is dead then and dies by itself.
+                self._deferred.append((rec, pol))
                 continue
-            rec.order = len(self._swapped)
-            self._swapped.append(weakref.ref(rec))
-            self._pending.append(rec)
-            self.swapped_tensors += 1
+            self._start_swap(rec, pol)
         if self.profile:
             ev = torch.cuda.Event(enable_timing=True)
             ev.record()
             self._prof_start = ev
+
+    def _start_swap(self, rec: _Record, pol: int) -> None:
+        try:
+            rec.ticket = self.mgr.swap_out(rec.tensor, pol)
+        except CswapError as err:
+            if err.status != 4:  # pools exhausted: this tensor simply stays on the device
+                raise
+            self.skipped_for_memory += 1
+            return
+        rec.order = len(self._swapped)
+        self._swapped.append(weakref.ref(rec))
+        self._pending.append(rec)
+        self.swapped_tensors += 1
 
     def post(self, x: TensorOrList, y: torch.Tensor, layer_type: LayerType = LayerType.ACT,
              isomit: bool = False, forward=None) -> None:
@@ -243,7 +274,7 @@ class Execution:
             # how to rebuild y should it be dropped: its producer and the producer's inputs
             # (a view of an input shares the input's record and is rebuilt with it)
             rec = self._record_for(y)
-            rec.producer = (forward, [self._pack(t) for t in inputs])
+            rec.producer = (forward, [self._ref(t) for t in inputs])
             self._produced.append(rec)
         if self.profile:
             ev = torch.cuda.Event(enable_timing=True)
@@ -254,6 +285,18 @@ class Execution:
                 "inputs": [getattr(t, "tensor_id", -1) for t in inputs], "omit": isomit,
                 "type": int(layer_type), "float32": y.dtype == torch.float32, "has_grad": y.grad_fn is not None,
             }
+            # which consumed tensors autograd holds on to once this consumer has run
+            for t in inputs:
+                tid = getattr(t, "tensor_id", -1)
+                if tid >= 0 and isinstance(t, torch.Tensor) and self._eligible(t):
+                    rec = self._records.get(t.untyped_storage().data_ptr())
+                    self._prof_saved[tid] = bool(rec is not None and rec.saved)
+        for rec, pol in self._deferred:
+            if rec.saved and rec.ticket is None and rec.tensor is not None:
+                self._start_swap(rec, pol)
+            elif not rec.saved:
+                self.skipped_unsaved += 1
+        self._deferred.clear()
         # the layer has run and saved what it needs: let go of the device copies
         for rec in self._pending:
             rec.tensor = None
@@ -269,9 +312,10 @@ class Execution:
                 "time_s": p["start"].elapsed_time(p["end"]) * 1e-3, "numel": p["numel"],
                 "zero_fraction": float(p["zero_fraction"]) if p["zero_fraction"] is not None else -1.0,
                 "inputs": p["inputs"], "omit": p["omit"], "type": p["type"], "float32": p["float32"],
-                "has_grad": p["has_grad"],
+                "has_grad": p["has_grad"], "saved": self._prof_saved.get(idx, True),
             }
         self._prof = {}
+        self._prof_saved = {}
         self.profile = False
         return out
 
@@ -310,6 +354,8 @@ class Execution:
             p = prof.get(tid)
             if p is None or p["omit"] or not p["float32"] or not p["has_grad"] or p["numel"] * 4 < min_bytes:
                 continue
+            if not p.get("saved", True):
+                continue  # nothing keeps it for backward: it dies after its consumer and costs no link time
             c = consumer[tid]
             cands.append(tid)
             descs.append(TensorDesc(p["numel"], p["zero_fraction"], tid in lossy, ready_s=start[c],

@@ -13,14 +13,23 @@ from ._lib import (CostModelStruct, MgrConfig, MgrStats, TensorDescStruct, Ticke
 from .codec import POLICY_RAW, POLICY_SPARSE, POLICY_ZFP, _require_cuda_f32, _stream_ptr
 
 
+class _Parked:
+    """Handle of a given-up ticket whose source tensor the device still reads."""
+    __slots__ = ("_h", "policy")
+
+    def __init__(self, h, policy):
+        self._h, self.policy = h, policy
+
+
 class Ticket:
     """One swapped-out tensor.  Holds the handle and what is needed to
     rebuild the tensor (shape, device)."""
 
-    __slots__ = ("_mgr", "_h", "shape", "numel", "device", "__weakref__")
+    __slots__ = ("_mgr", "_h", "shape", "numel", "device", "policy", "__weakref__")
 
-    def __init__(self, mgr: "SwapManager", handle: int, shape, numel: int, device):
+    def __init__(self, mgr: "SwapManager", handle: int, shape, numel: int, device, policy: int = -1):
         self._mgr, self._h, self.shape, self.numel, self.device = mgr, handle, tuple(shape), numel, device
+        self.policy = policy  # as requested by the caller
 
     @property
     def alive(self) -> bool:
@@ -33,14 +42,19 @@ class Ticket:
                 "complete": bool(ti.complete)}
 
     def release(self) -> None:
-        """Give the ticket up; its pool memory returns once its copies have finished."""
+        """Give the ticket up; its pool memory returns once its copies have
+        finished.  Never blocks: if the device is still reading the source
+        tensor, ticket and tensor are parked and retired by a later call."""
         mgr = self._mgr
         if self._h is not None and mgr._h is not None:
-            if any(tk is self for tk, _ in mgr._reading):
-                # the source tensor is still held for the device's sake: it may
-                # only be dropped once the device has finished reading it
-                check(lib().csw_swap_out_sync(mgr._h, self._h), "csw_swap_out_sync")
-                mgr._reading = [(tk, t) for tk, t in mgr._reading if tk is not self]
+            for i, (tk, t) in enumerate(mgr._reading):
+                if tk is self:
+                    del mgr._reading[i]
+                    if not mgr.out_done(self):
+                        mgr._retiring.append((_Parked(self._h, self.policy), t))
+                        self._h = None
+                        return
+                    break
             check(lib().csw_ticket_release(mgr._h, self._h), "csw_ticket_release")
         self._h = None
 
@@ -70,16 +84,71 @@ class SwapManager:
         # block to someone else; it is dropped at the first call after the
         # device has finished reading.
         self._reading: List[Tuple[Ticket, torch.Tensor]] = []
+        # Tickets given up (or whose tensor was taken back) before the copy out had
+        # finished, with the tensor they read: released once the device is done
+        # with them, never waited for.
+        self._retiring: list = []
+        self.reclaimed_tensors = 0
 
     def close(self) -> None:
         if self._h is not None:
             check(lib().csw_mgr_destroy(self._h), "csw_mgr_destroy")  # drains the manager's streams
             self._h = None
             self._reading.clear()
+            for tk, _ in self._retiring:
+                tk._h = None  # the manager and its tickets are gone
+            self._retiring.clear()
 
     def _poll(self) -> None:
+        """Drop source tensors the device has finished reading and retire parked
+        tickets.  Raw swap-outs finish in order on the copy stream and coded
+        ones in order on the codec stream, so each kind is only asked about
+        until the first one that is still busy."""
         if self._reading:
-            self._reading = [(tk, t) for tk, t in self._reading if tk._h is not None and not self.out_done(tk)]
+            busy = set()
+            keep = []
+            for tk, t in self._reading:
+                if tk._h is None:
+                    continue
+                kind = tk.policy == POLICY_RAW
+                if kind in busy or not self.out_done(tk):
+                    busy.add(kind)
+                    keep.append((tk, t))
+            self._reading = keep
+        if self._retiring:
+            busy = set()
+            keep = []
+            for tk, t in self._retiring:
+                if tk._h is None:
+                    continue
+                kind = getattr(tk, "policy", None) == POLICY_RAW
+                if kind in busy or not self.out_done(tk):
+                    busy.add(kind)
+                    keep.append((tk, t))
+                else:
+                    check(lib().csw_ticket_release(self._h, tk._h), "csw_ticket_release")
+                    tk._h = None
+            self._retiring = keep
+
+    def reclaim(self, ticket: Ticket) -> Optional[torch.Tensor]:
+        """The swapped-out tensor itself, if it has not left yet: while the
+        copy out of a losslessly swapped tensor is still queued or running the
+        device copy is intact (the manager only reads it), so a consumer that
+        needs it now can simply take it back instead of waiting for the copy
+        out and a copy in.  The ticket is retired in the background.  None when
+        the device copy is gone or the policy is lossy (a lossy swap must hand
+        back the decoded values whatever the timing)."""
+        if ticket._h is None or ticket.policy not in (POLICY_RAW, POLICY_SPARSE):
+            return None
+        for i, (tk, t) in enumerate(self._reading):
+            if tk is ticket:
+                if self.out_done(ticket):
+                    return None
+                del self._reading[i]
+                self._retiring.append((ticket, t))
+                self.reclaimed_tensors += 1
+                return t
+        return None
 
     def raw_streams(self) -> Tuple[int, int, int]:
         """(codec, d2h, h2d) cudaStream_t handles of the manager."""
@@ -103,7 +172,7 @@ class SwapManager:
         h = C.c_void_p()
         check(lib().csw_swap_out(self._h, t.data_ptr(), t.numel(), policy, _stream_ptr(t.device), C.byref(h)),
               "csw_swap_out")
-        tk = Ticket(self, h.value, t.shape, t.numel(), t.device)
+        tk = Ticket(self, h.value, t.shape, t.numel(), t.device, policy)
         self._poll()
         self._reading.append((tk, t))
         return tk
@@ -140,6 +209,7 @@ class SwapManager:
 
     def sync(self) -> None:
         check(lib().csw_mgr_sync(self._h), "csw_mgr_sync")
+        self._poll()
 
 
 @dataclass

@@ -111,6 +111,7 @@ class Execution {
   }
 
   int index = -1;
+  long reclaimed = 0;  // tensors taken back before they had left the device
   std::vector<int> policy;
   std::vector<int> begin_stage;
   std::vector<Layer_type> types;
@@ -124,6 +125,7 @@ class Execution {
     csw_ticket* ticket = nullptr;
     size_t nbytes = 0;
     int order = -1;         // position among this step's swap-outs
+    int policy = 0;
     bool restored = false;
     at::DataPtr reading;    // the device block while the manager still reads it
     ~Swapped() {
@@ -169,6 +171,7 @@ class Execution {
                                        c10::cuda::getCurrentCUDAStream().stream(), &s->ticket);
     if (st == CSW_ERR_NOMEM) return;  // pools exhausted: the tensor stays on the device
     check(st, "csw_swap_out");
+    s->policy = pol;
     s->order = (int)order_.size();
     order_.push_back(s);
     pending_.push_back(s);
@@ -196,6 +199,20 @@ class Execution {
   }
 
   void restore(Swapped& s) {
+    // A losslessly swapped tensor that is needed again before the manager has
+    // finished reading it never left the device: hand the block back as it is.
+    // (A lossy one must come back as the decoded values whatever the timing.)
+    if (s.reading.get() != nullptr && (s.policy == CSW_POLICY_RAW || s.policy == CSW_POLICY_SPARSE)) {
+      int done = 1;
+      csw_swap_out_done(mgr_, s.ticket, &done);
+      if (!done) {
+        s.storage->set_data_ptr_noswap(std::move(s.reading));
+        s.restored = true;
+        reclaimed++;
+        poll();
+        return;
+      }
+    }
     auto* alloc = c10::cuda::CUDACachingAllocator::get();
     at::DataPtr dp = alloc->allocate(s.nbytes);
     check(csw_swap_in(mgr_, s.ticket, static_cast<float*>(dp.get()), c10::cuda::getCurrentCUDAStream().stream()),
@@ -218,6 +235,7 @@ class Execution {
     size_t k = 0;
     for (auto& s : reading_) {
       int done = 1;
+      if (s->restored && s->reading.get() == nullptr) continue;  // taken back: the storage owns the block again
       if (s->ticket) csw_swap_out_done(mgr_, s->ticket, &done);
       if (done) s->reading.clear();
       else reading_[k++] = s;

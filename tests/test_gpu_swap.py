@@ -37,6 +37,45 @@ def test_raw_roundtrip(cs, mgr):
     assert s["swap_outs"] == 1 and s["swap_ins"] == 1 and s["pinned_in_use"] == 0 and s["staging_in_use"] == 0
 
 
+def test_reclaim_before_departure_and_nonblocking_release(cs):
+    """A losslessly swapped tensor that is wanted back while its copy out is
+    still running is handed back as it is (no copy in); a lossy one never is;
+    giving a ticket up while the device still reads its tensor does not block,
+    and everything is returned to the pools once the copies have finished."""
+    import time
+    import torch
+    m = cs.SwapManager(pinned_bytes=1 << 30, staging_bytes=256 << 20)
+    big = torch.randn(64 << 20, device="cuda")       # 256 MiB: several ms on the host link
+    keep = big.clone()
+    torch.cuda.synchronize()
+    tk = m.swap_out(big, cs.POLICY_RAW)
+    back = m.reclaim(tk)
+    assert back is big and m.reclaimed_tensors == 1   # the copy out cannot have finished yet
+    assert m.reclaim(tk) is None                      # only once
+    tz = m.swap_out(big, cs.POLICY_ZFP)
+    assert m.reclaim(tz) is None                      # lossy: must come back decoded
+    tr = m.swap_out(big, cs.POLICY_RAW)
+    t0 = time.perf_counter()
+    tr.release()                                      # still being read: parked, not waited for
+    assert time.perf_counter() - t0 < 2e-3
+    m.sync()
+    torch.cuda.synchronize()
+    assert torch.equal(big, keep)                     # the manager only ever read it
+    dec = m.swap_in(tz)
+    torch.cuda.synchronize()
+    assert torch.equal(dec, cs.zfp_decompress(cs.zfp_compress(keep, 512), keep.numel(), 512))
+    tz.release()
+    done = m.swap_out(big, cs.POLICY_RAW)
+    m.sync()
+    assert m.reclaim(done) is None                    # it has left: a real swap-in is needed
+    assert torch.equal(m.swap_in(done), keep)
+    done.release()
+    m.sync()
+    s = m.stats()
+    assert s["pinned_in_use"] == 0 and s["staging_in_use"] == 0 and not m._retiring and not m._reading
+    m.close()
+
+
 def test_zfp_matches_codec(cs, mgr):
     import torch
     t = torch.from_numpy(util.tanh_normal(4 << 20, 2)).cuda()
@@ -189,7 +228,9 @@ def test_execution_lossless_policies_do_not_change_training(cs):
     base_loss, base_grads, _, _ = _step(cs, torch, net, x, y, lambda i, l: cs.POLICY_KEEP)
     for pol in (cs.POLICY_RAW, cs.POLICY_SPARSE):
         loss, grads, stats, exe = _step(cs, torch, net, x, y, lambda i, l: pol)
-        assert exe.swapped_tensors >= 6 and stats["swap_ins"] >= 4  # not every swapped tensor is needed again
+        # conv outputs feed ReLUs, which keep their own output: nobody saves them, so they are not copied out
+        assert exe.swapped_tensors >= 5 and exe.skipped_unsaved >= 3
+        assert stats["swap_ins"] == exe.swapped_tensors  # everything that went out was needed again
         assert loss == base_loss
         for g, b in zip(grads, base_grads):
             assert torch.equal(g, b)
