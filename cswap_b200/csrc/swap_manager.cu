@@ -225,14 +225,21 @@ void poll(csw_mgr* m) {
   }
   m->zombies.resize(z);
   size_t k = 0;
+  // `live` is in submission order and every copy out goes down the one D2H
+  // stream, so behind the first unfinished one none has finished either
+  bool d2h_busy = false;
   for (size_t i = 0; i < m->live.size(); i++) {
     csw_ticket* t = m->live[i];
     bool keep = true;
-    if (t->state == T_OUT && cudaEventQuery(t->ev_d2h) == cudaSuccess) {
-      if (t->policy == CSW_POLICY_SPARSE) finalize_moved(m, t);
-      free_stage(m, t);
-      t->state = T_HOST;
-      keep = false;
+    if (t->state == T_OUT) {
+      if (!d2h_busy && cudaEventQuery(t->ev_d2h) == cudaSuccess) {
+        if (t->policy == CSW_POLICY_SPARSE) finalize_moved(m, t);
+        free_stage(m, t);
+        t->state = T_HOST;
+        keep = false;
+      } else {
+        d2h_busy = true;
+      }
     } else if (t->state == T_IN && t->ev_done && cudaEventQuery(t->ev_done) == cudaSuccess) {
       free_stage(m, t);
       t->state = T_HOST;
