@@ -11,7 +11,7 @@ from .codec import (  # noqa: F401
     sparse_layout, sparse_compress, sparse_decompress, sparse_packed_bytes,
     legacy_sparse_compress, legacy_sparse_decompress,
 )
-from .swap import SwapManager, Ticket, CostModel, TensorDesc  # noqa: F401
+from .swap import SwapManager, Ticket, CostModel, TensorDesc, blob_info  # noqa: F401
 from .execution import Execution, LayerType  # noqa: F401
 
 __version__ = "0.1.0"

@@ -33,6 +33,12 @@ class TicketInfo(C.Structure):
                 ("complete", C.c_int)]
 
 
+class BlobHeader(C.Structure):
+    _fields_ = [("magic", C.c_uint32), ("version", C.c_uint32), ("policy", C.c_uint32), ("zfp_maxbits", C.c_uint32),
+                ("numel", C.c_uint64), ("payload_bytes", C.c_uint64), ("nnz", C.c_uint64),
+                ("reserved", C.c_uint64 * 3)]
+
+
 class MgrStats(C.Structure):
     _fields_ = [("swap_outs", C.c_uint64), ("swap_ins", C.c_uint64), ("raw_bytes_out", C.c_uint64),
                 ("moved_bytes_out", C.c_uint64), ("raw_bytes_in", C.c_uint64), ("moved_bytes_in", C.c_uint64),
@@ -110,6 +116,9 @@ SIGNATURES = {
     "csw_swap_in": (_I, [_P, _P, _P, _P]),
     "csw_ticket_release": (_I, [_P, _P]),
     "csw_ticket_query": (_I, [_P, _P, C.POINTER(TicketInfo)]),
+    "csw_ticket_export": (_I, [_P, _P, _P, _SZ, C.POINTER(_SZ)]),
+    "csw_blob_info": (_I, [_P, _SZ, C.POINTER(BlobHeader)]),
+    "csw_blob_import": (_I, [_P, _P, _SZ, C.POINTER(_P)]),
     "csw_mgr_get_stats": (_I, [_P, C.POINTER(MgrStats)]),
     "csw_mgr_reset_stats": (_I, [_P]),
     "csw_mgr_sync": (_I, [_P]),

@@ -24,6 +24,7 @@
 
 #include "../../include/cswap_b200.h"
 #include "internal.h"
+#include "sparse_kernels.h"
 
 namespace csw {
 namespace {
@@ -522,7 +523,7 @@ static csw_status load_stage(csw_mgr* m, csw_ticket* t) {
     e = get_event(m, &t->ev_h2d);
     if (e != cudaSuccess) return cuda_fail(e);
   }
-  e = cudaStreamWaitEvent(m->s_h2d, t->ev_d2h, 0);
+  e = t->ev_d2h ? cudaStreamWaitEvent(m->s_h2d, t->ev_d2h, 0) : cudaSuccess;  // imported tickets have no copy out
   if (e == cudaSuccess) e = cudaMemcpyAsync(t->stage, t->host, t->moved, cudaMemcpyHostToDevice, m->s_h2d);
   if (e == cudaSuccess) e = cudaEventRecord(t->ev_h2d, m->s_h2d);
   if (e != cudaSuccess) return cuda_fail(e);
@@ -562,7 +563,7 @@ csw_status csw_swap_in(csw_mgr* m, csw_ticket* t, float* d_dst, csw_stream_t com
   const size_t raw = t->numel * sizeof(float);
   csw_status st = CSW_OK;
   if (t->policy == CSW_POLICY_RAW) {
-    e = cudaStreamWaitEvent(m->s_h2d, t->ev_d2h, 0);
+    e = t->ev_d2h ? cudaStreamWaitEvent(m->s_h2d, t->ev_d2h, 0) : cudaSuccess;
     if (e == cudaSuccess) e = cudaMemcpyAsync(d_dst, t->host, raw, cudaMemcpyHostToDevice, m->s_h2d);
     if (e == cudaSuccess) e = cudaEventRecord(t->ev_done, m->s_h2d);
   } else {
@@ -617,6 +618,114 @@ csw_status csw_ticket_query(csw_mgr* m, csw_ticket* t, csw_ticket_info* info) {
   info->raw_bytes = t->numel * sizeof(float);
   info->moved_bytes = t->moved;
   info->complete = t->moved_final ? 1 : 0;
+  return CSW_OK;
+}
+
+// ---- self-describing blobs ---------------------------------------------------------
+static_assert(sizeof(csw_blob_header) == 64, "blob header layout");
+
+static inline int popcount32(uint32_t v) { return __builtin_popcount(v); }
+
+csw_status csw_blob_info(const void* blob, size_t bytes, csw_blob_header* header) {
+  if (!blob || !header) return CSW_ERR_ARG;
+  if (bytes < sizeof(csw_blob_header)) return CSW_ERR_SIZE;
+  csw_blob_header h;
+  std::memcpy(&h, blob, sizeof h);
+  if (h.magic != CSW_BLOB_MAGIC || h.version != CSW_BLOB_VERSION || h.numel == 0) return CSW_ERR_ARG;
+  if (bytes - sizeof h < h.payload_bytes) return CSW_ERR_SIZE;
+  const unsigned char* payload = static_cast<const unsigned char*>(blob) + sizeof h;
+  if (h.policy == CSW_POLICY_RAW) {
+    if (h.payload_bytes != h.numel * sizeof(float) || h.nnz != 0 || h.zfp_maxbits != 0) return CSW_ERR_ARG;
+  } else if (h.policy == CSW_POLICY_ZFP) {
+    size_t nz = 0, zbytes = 0;
+    if (zfp_geometry(h.numel, h.zfp_maxbits, &nz, &zbytes) != CSW_OK || h.payload_bytes != zbytes || h.nnz != 0)
+      return CSW_ERR_ARG;
+  } else if (h.policy == CSW_POLICY_SPARSE) {
+    csw_sparse_layout L;
+    if (csw_sparse_layout_of(h.numel, &L) != CSW_OK || h.zfp_maxbits != 0 || h.nnz > h.numel ||
+        h.payload_bytes != L.values + 4 * h.nnz)
+      return CSW_ERR_ARG;
+    // every tile's segment must lie inside the packed values: the unpack kernel
+    // trusts tile_off, so a damaged blob is turned away here, on the host
+    const size_t tiles = (h.numel + SPARSE_TILE - 1) / SPARSE_TILE, words = (h.numel + 31) / 32;
+    uint64_t total = 0;
+    for (size_t t = 0; t < tiles; t++) {
+      uint32_t off;
+      std::memcpy(&off, payload + L.tile_off + 4 * t, 4);
+      const size_t w0 = t * (SPARSE_TILE / 32), w1 = w0 + SPARSE_TILE / 32 < words ? w0 + SPARSE_TILE / 32 : words;
+      uint32_t cnt = 0;
+      for (size_t w = w0; w < w1; w++) {
+        uint32_t bits;
+        std::memcpy(&bits, payload + L.bitmap + 4 * w, 4);
+        if (w == words - 1 && (h.numel & 31)) bits &= (1u << (h.numel & 31)) - 1u;
+        cnt += (uint32_t)popcount32(bits);
+      }
+      if ((uint64_t)off + cnt > h.nnz) return CSW_ERR_ARG;
+      total += cnt;
+    }
+    if (total != h.nnz) return CSW_ERR_ARG;
+  } else {
+    return CSW_ERR_ARG;
+  }
+  *header = h;
+  return CSW_OK;
+}
+
+csw_status csw_ticket_export(csw_mgr* m, csw_ticket* t, void* dst, size_t cap, size_t* bytes) {
+  if (!m || !t || !bytes) return CSW_ERR_ARG;
+  std::lock_guard<std::mutex> lk(m->mu);
+  DeviceGuard g(m->device);
+  if (t->state == T_DEAD) return CSW_ERR_STATE;
+  if (t->ev_d2h) {
+    cudaError_t e = cudaEventSynchronize(t->ev_d2h);
+    if (e != cudaSuccess) return cuda_fail(e);
+  }
+  if (!t->moved_final) finalize_moved(m, t);
+  const size_t total = sizeof(csw_blob_header) + t->moved;
+  *bytes = total;
+  if (!dst) return CSW_OK;
+  if (cap < total) return CSW_ERR_SIZE;
+  csw_blob_header h{};
+  h.magic = CSW_BLOB_MAGIC;
+  h.version = CSW_BLOB_VERSION;
+  h.policy = (uint32_t)t->policy;
+  h.zfp_maxbits = t->policy == CSW_POLICY_ZFP ? t->maxbits : 0u;
+  h.numel = t->numel;
+  h.payload_bytes = t->moved;
+  if (t->policy == CSW_POLICY_SPARSE) {
+    csw_sparse_layout L;
+    csw_sparse_layout_of(t->numel, &L);
+    h.nnz = (t->moved - L.values) / 4;
+  }
+  std::memcpy(dst, &h, sizeof h);
+  std::memcpy(static_cast<char*>(dst) + sizeof h, t->host, t->moved);
+  return CSW_OK;
+}
+
+csw_status csw_blob_import(csw_mgr* m, const void* blob, size_t bytes, csw_ticket** ticket) {
+  if (!m || !ticket) return CSW_ERR_ARG;
+  csw_blob_header h;
+  csw_status st = csw_blob_info(blob, bytes, &h);
+  if (st != CSW_OK) return st;
+  std::lock_guard<std::mutex> lk(m->mu);
+  DeviceGuard g(m->device);
+  if (!g.ok) return CSW_ERR_ARG;
+  poll(m);
+  csw_ticket* t = new (std::nothrow) csw_ticket;
+  if (!t) return CSW_ERR_NOMEM;
+  t->policy = (int)h.policy;
+  t->numel = (size_t)h.numel;
+  t->maxbits = h.zfp_maxbits;
+  t->state = T_HOST;
+  t->moved = (size_t)h.payload_bytes;
+  t->moved_final = true;
+  t->host = pool_alloc(m, m->pinned, t->moved, &t->host_cap);
+  if (!t->host) {
+    delete t;
+    return CSW_ERR_NOMEM;
+  }
+  std::memcpy(t->host, static_cast<const char*>(blob) + sizeof h, t->moved);
+  *ticket = t;
   return CSW_OK;
 }
 

@@ -9,8 +9,18 @@ from typing import Iterable, List, Optional, Sequence, Tuple
 
 import torch
 
-from ._lib import (CostModelStruct, MgrConfig, MgrStats, TensorDescStruct, TicketInfo, check, lib)
+from ._lib import (BlobHeader, CostModelStruct, MgrConfig, MgrStats, TensorDescStruct, TicketInfo, check, lib)
 from .codec import POLICY_RAW, POLICY_SPARSE, POLICY_ZFP, _require_cuda_f32, _stream_ptr
+
+
+def blob_info(blob) -> dict:
+    """Header of a self-describing blob after validation (needs no GPU)."""
+    import numpy as np
+    a = np.ascontiguousarray(np.frombuffer(blob, dtype=np.uint8) if not isinstance(blob, np.ndarray) else blob)
+    h = BlobHeader()
+    check(lib().csw_blob_info(a.ctypes.data, a.size, C.byref(h)), "csw_blob_info")
+    return {"policy": h.policy, "numel": h.numel, "zfp_maxbits": h.zfp_maxbits, "payload_bytes": h.payload_bytes,
+            "nnz": h.nnz, "version": h.version}
 
 
 class _Parked:
@@ -40,6 +50,18 @@ class Ticket:
         check(lib().csw_ticket_query(self._mgr._h, self._h, C.byref(ti)), "csw_ticket_query")
         return {"policy": ti.policy, "numel": ti.numel, "raw_bytes": ti.raw_bytes, "moved_bytes": ti.moved_bytes,
                 "complete": bool(ti.complete)}
+
+    def export(self):
+        """The swapped-out tensor as a self-describing blob (numpy uint8 array):
+        a 64-byte header (policy, element count, zfp bits per block, sparse
+        count) and the payload as it crossed the link.  Waits for the copy out."""
+        import numpy as np
+        n = C.c_size_t()
+        check(lib().csw_ticket_export(self._mgr._h, self._h, None, 0, C.byref(n)), "csw_ticket_export")
+        buf = np.empty(n.value, dtype=np.uint8)
+        check(lib().csw_ticket_export(self._mgr._h, self._h, buf.ctypes.data, buf.size, C.byref(n)),
+              "csw_ticket_export")
+        return buf
 
     def release(self) -> None:
         """Give the ticket up; its pool memory returns once its copies have
@@ -176,6 +198,18 @@ class SwapManager:
         self._poll()
         self._reading.append((tk, t))
         return tk
+
+    def import_blob(self, blob, shape=None) -> Ticket:
+        """A ticket for a blob made by Ticket.export (here or in another
+        process): swap_in() then rebuilds the tensor on this device."""
+        import numpy as np
+        a = np.ascontiguousarray(np.frombuffer(blob, dtype=np.uint8) if not isinstance(blob, np.ndarray) else blob)
+        info = blob_info(a)
+        h = C.c_void_p()
+        check(lib().csw_blob_import(self._h, a.ctypes.data, a.size, C.byref(h)), "csw_blob_import")
+        numel = info["numel"]
+        return Ticket(self, h.value, tuple(shape) if shape is not None else (numel,), numel, self.device,
+                      info["policy"])
 
     def out_done(self, ticket: Ticket) -> bool:
         d = C.c_int()

@@ -229,6 +229,36 @@ typedef struct {
 } csw_ticket_info;
 csw_status csw_ticket_query(csw_mgr* m, csw_ticket* t, csw_ticket_info* info);
 
+/* Self-describing form of a swapped-out tensor: a 64-byte header followed by
+ * the payload exactly as it crossed the host link (raw floats, a ZFP stream, or
+ * the packed sparse buffer).  The reference keeps rate, sizes and the sparse
+ * side buffers only in live C++ objects (CSWAP+/Execution.h:98-102,115), so a
+ * swapped tensor cannot outlive its process; a blob can be written to disk,
+ * handed to another process or replica, and swapped in there. */
+#define CSW_BLOB_MAGIC 0x50575343u /* "CSWP" */
+#define CSW_BLOB_VERSION 1u
+typedef struct {
+  uint32_t magic, version;
+  uint32_t policy;        /* CSW_POLICY_RAW / _SPARSE / _ZFP */
+  uint32_t zfp_maxbits;   /* bits per zfp block, 0 unless policy is ZFP */
+  uint64_t numel;         /* float32 elements of the tensor */
+  uint64_t payload_bytes; /* bytes that follow the header */
+  uint64_t nnz;           /* sparse: packed values; otherwise 0 */
+  uint64_t reserved[3];
+} csw_blob_header;        /* 64 bytes */
+/* Copy header + payload of a ticket to dst (any host memory).  Waits for the
+ * ticket's copy out to finish.  *bytes receives the size; with dst == NULL
+ * only the size is reported.  CSW_ERR_SIZE if cap is too small. */
+csw_status csw_ticket_export(csw_mgr* m, csw_ticket* t, void* dst, size_t cap, size_t* bytes);
+/* Check a blob (magic, version, policy, sizes; for sparse payloads also that
+ * every tile's segment lies inside the packed values) and return its header.
+ * Needs no GPU. */
+csw_status csw_blob_info(const void* blob, size_t bytes, csw_blob_header* header);
+/* Turn a blob back into a ticket that lives in the manager's pinned pool, as
+ * if the tensor had just been swapped out; csw_swap_in / csw_prefetch /
+ * csw_ticket_release then work as usual.  Rejects blobs csw_blob_info rejects. */
+csw_status csw_blob_import(csw_mgr* m, const void* blob, size_t bytes, csw_ticket** ticket);
+
 typedef struct {
   uint64_t swap_outs, swap_ins;
   uint64_t raw_bytes_out, moved_bytes_out; /* uncompressed vs. on-link, swap-out */

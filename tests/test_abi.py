@@ -96,3 +96,52 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(lib, "LIB_PATH", "/nonexistent/libcswap_b200.so")
     with pytest.raises(lib.LibraryMissing):
         lib.lib()
+
+
+def test_blob_header_validation_without_a_device(L):
+    """csw_blob_info is host logic: sizes, policy, and for sparse payloads the
+    consistency of tile offsets with the bitmap."""
+    import ctypes as C
+    import struct
+    import numpy as np
+    import cswap_b200 as cs
+    from cswap_b200._lib import SparseLayout
+
+    def blob(policy, numel, payload, maxbits=0, nnz=0, magic=0x50575343, version=1):
+        return np.frombuffer(struct.pack("<IIIIQQQ3Q", magic, version, policy, maxbits, numel, len(payload), nnz,
+                                         0, 0, 0) + bytes(payload), dtype=np.uint8)
+
+    raw = blob(2, 8, bytes(32))
+    assert cs.blob_info(raw) == {"policy": 2, "numel": 8, "zfp_maxbits": 0, "payload_bytes": 32, "nnz": 0,
+                                 "version": 1}
+    for bad in (blob(2, 8, bytes(28)), blob(2, 8, bytes(32), magic=1), blob(2, 8, bytes(32), version=2),
+                blob(5, 8, bytes(32)), blob(2, 0, b""), blob(2, 8, bytes(32), nnz=1)):
+        with pytest.raises(cs.CswapError):
+            cs.blob_info(bad)
+    with pytest.raises(cs.CswapError):
+        cs.blob_info(raw[:40])                               # shorter than the header
+    with pytest.raises(cs.CswapError):
+        cs.blob_info(raw[:-1])                               # payload cut short
+    # zfp: 4096 values = 32x32x4 = 64 blocks of 512 bits
+    assert cs.blob_info(blob(6, 4096, bytes(4096), maxbits=512))["zfp_maxbits"] == 512
+    with pytest.raises(cs.CswapError):
+        cs.blob_info(blob(6, 4000, bytes(4096), maxbits=512))  # not a whole number of 32x32 slabs
+    with pytest.raises(cs.CswapError):
+        cs.blob_info(blob(6, 4096, bytes(2048), maxbits=512))
+    # sparse: 5000 elements, two tiles, non-zeros at 3, 40 and 4100
+    n = 5000
+    lay = SparseLayout()
+    assert L.csw_sparse_layout_of(n, C.byref(lay)) == 0
+    def sparse(tile_off, nnz):
+        p = bytearray(lay.values + 4 * nnz)
+        p[lay.tile_off:lay.tile_off + 8] = struct.pack("<II", *tile_off)
+        words = np.zeros((n + 31) // 32, dtype=np.uint32)
+        for i in (3, 40, 4100):
+            words[i // 32] |= np.uint32(1 << (i % 32))
+        p[lay.bitmap:lay.bitmap + 4 * words.size] = words.tobytes()
+        return blob(3, n, p, nnz=nnz)
+    assert cs.blob_info(sparse((0, 2), 3))["nnz"] == 3
+    assert cs.blob_info(sparse((1, 0), 3))["nnz"] == 3       # segments in schedule order are fine
+    for bad in (sparse((0, 3), 3), sparse((2, 0), 3), sparse((0, 2), 4), sparse((0, 2), 2)):
+        with pytest.raises(cs.CswapError):
+            cs.blob_info(bad)

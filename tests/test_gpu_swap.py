@@ -76,6 +76,52 @@ def test_reclaim_before_departure_and_nonblocking_release(cs):
     m.close()
 
 
+def test_blob_export_import_roundtrip(cs, tmp_path):
+    """A swapped-out tensor written out as a self-describing blob and brought
+    back through a different manager gives what swap_in of the original ticket
+    would have given, for all three policies."""
+    import numpy as np
+    import torch
+    a = cs.SwapManager(pinned_bytes=256 << 20, staging_bytes=128 << 20)
+    b = cs.SwapManager(pinned_bytes=256 << 20, staging_bytes=128 << 20, zfp_maxbits=256)  # its own rate is irrelevant
+    n = 3 * 1024 * 1024
+    dense = torch.tanh(torch.randn(n, device="cuda"))
+    relu = torch.relu(torch.randn(n, device="cuda") - 0.6)
+    cases = [(cs.POLICY_RAW, dense, dense), (cs.POLICY_SPARSE, relu, relu),
+             (cs.POLICY_ZFP, dense, cs.zfp_decompress(cs.zfp_compress(dense, 512), n, 512))]
+    for pol, src, want in cases:
+        tk = a.swap_out(src, pol)
+        blob = tk.export()
+        info = cs.blob_info(blob)
+        assert info["policy"] == pol and info["numel"] == n and blob.size == 64 + info["payload_bytes"]
+        assert info["zfp_maxbits"] == (512 if pol == cs.POLICY_ZFP else 0)
+        if pol == cs.POLICY_SPARSE:
+            assert info["nnz"] == int(torch.count_nonzero(relu).item())
+        assert info["payload_bytes"] == tk.info()["moved_bytes"]
+        tk.release()
+        path = tmp_path / f"t{pol}.cswp"
+        blob.tofile(path)                                     # outlives the ticket and the manager that made it
+        tk2 = b.import_blob(np.fromfile(path, dtype=np.uint8), shape=(3, 1024, 1024))
+        back = b.swap_in(tk2)
+        torch.cuda.synchronize()
+        assert back.shape == (3, 1024, 1024) and torch.equal(back.view(-1).view(torch.int32), want.view(torch.int32))
+        tk2.release()
+    # a damaged sparse blob is refused on the host, nothing is launched
+    tk = a.swap_out(relu, cs.POLICY_SPARSE)
+    blob = tk.export()
+    tk.release()
+    L = cs.sparse_layout(n)
+    bad = blob.copy()
+    bad[64 + L.tile_off + 4:64 + L.tile_off + 8] = np.frombuffer(np.uint32(n).tobytes(), dtype=np.uint8)
+    with pytest.raises(cs.CswapError):
+        b.import_blob(bad)
+    a.sync()
+    b.sync()
+    assert a.stats()["pinned_in_use"] == 0 and b.stats()["pinned_in_use"] == 0
+    a.close()
+    b.close()
+
+
 def test_zfp_matches_codec(cs, mgr):
     import torch
     t = torch.from_numpy(util.tanh_normal(4 << 20, 2)).cuda()
