@@ -336,6 +336,49 @@ def test_execution_baseline_planners(cs):
     assert loss == base_loss and all(torch.equal(g, b) for g, b in zip(grads, base_grads))
 
 
+def test_reference_python_hook_names(cs):
+    """The torch.cswap* call pattern of the reference's model zoo
+    (CIFAR10/models/vgg.py:23-46) on stock PyTorch."""
+    import types
+    import torch
+    import cswap_b200.compat as compat
+    ns = types.SimpleNamespace()
+    compat.install(ns)
+    net = _small_net(torch)
+    x = torch.randn(64, 3, 32, 32, device="cuda")
+    y = torch.randint(0, 10, (64,), device="cuda")
+    torch.backends.cudnn.deterministic = True
+
+    def run(type_for):
+        for p in net.parameters():
+            p.grad = None
+        ns.cswapinit()
+        out = x
+        for layer in net:
+            t = type_for(layer)
+            pre = out
+            ns.cswappre(pre, t)
+            out = layer(pre)
+            ns.cswappost(pre, out, t)
+        loss = torch.nn.functional.cross_entropy(out, y)
+        loss.backward()
+        torch.cuda.synchronize()
+        return float(loss.detach()), [p.grad.clone() for p in net.parameters()]
+
+    ns.cswapinit_()
+    ns.cswapsetratio(512)
+    base = run(lambda l: 0)
+    mgr = compat.execution().mgr
+    before = mgr.stats()["swap_outs"]
+    got = run(lambda l: 2 if isinstance(l, torch.nn.Conv2d) else 3)   # "2 = vDNN" on conv inputs, ZVC elsewhere
+    assert mgr.stats()["swap_outs"] - before >= 4
+    assert got[0] == base[0] and all(torch.equal(a, b) for a, b in zip(got[1], base[1]))
+    lossy = run(lambda l: 6 if isinstance(l, torch.nn.Conv2d) else 0)  # "6 = ZFP"
+    assert abs(lossy[0] - base[0]) < 1e-3 and not all(torch.equal(a, b) for a, b in zip(lossy[1], base[1]))
+    compat.execution().postforward()
+    mgr.close()
+
+
 def test_execution_zfp_equals_codec_applied_to_activations(cs):
     """With policy 6 on one tensor, backward sees exactly decode(encode(x))."""
     import torch
