@@ -6,7 +6,8 @@
 //
 //  * slab kernels for the swap path's view (nx = ny = 32, contiguous, whole
 //    32-bit words per block): one CTA per group of 8 z-slabs (32 KiB, 128
-//    blocks), four CTAs per SM, lane = zfp block held in registers.  A lane moves its block with
+//    blocks), four (encoder) or five (decoder) CTAs per SM, lane = zfp block held
+//    in registers.  A lane moves its block with
 //    sixteen 128-bit accesses (eight neighbouring lanes cover one 128-byte row
 //    segment, so a warp access touches four whole lines); stream words sit
 //    word-major in shared memory (bank = lane, so diverged lanes never
@@ -34,7 +35,9 @@ namespace {
 constexpr int kThreads = 128;                  // zfp blocks (lanes) per CTA
 constexpr int kSlabFloats = 1024;              // one 32x32 z-slab
 constexpr int kGroupSlabs = kThreads / 16;      // z-slabs per CTA: kThreads / 64 tiles of four
-constexpr int kCtasPerSm = 512 / kThreads;      // by registers (128 per thread)
+constexpr int kEncCtasPerSm = 4;                // 128 registers per thread: the encoder needs 122
+constexpr int kDecCtasPerSm = 5;                // 96 registers: the decoder fits without spills, and a fifth
+                                                // CTA hides more of its dependent shared-memory reads
 
 // ---- word staging: word w of the block owned by thread t lives at [w * kThreads + t] --
 // Staged stream words of the decoder: rows nwords and nwords + 1 are kept zero
@@ -72,7 +75,7 @@ __device__ __forceinline__ int pad_src_z(int z, int vz) { return z < vz ? z : (z
 // 128-byte row segment, so a warp load touches four full lines), codes it into
 // its own column of the word-major staging area and writes its own words out:
 // after the table is built no warp waits for another.
-__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+__global__ void __launch_bounds__(kThreads, kEncCtasPerSm)
 zfp_encode_slab_kernel(const float* __restrict__ in, uint32_t* __restrict__ out, uint32_t nz, int maxbits,
                        const PipeConsts kc) {
   extern __shared__ __align__(16) uint32_t smem_words[];
@@ -144,7 +147,7 @@ static_assert(DEC_LUT_SIZE % (4 * kThreads) == 0, "table copy assumes whole 128-
 // lane pulls its own compressed words into its column of the word-major staging
 // area, parses them by bit position and stores the rebuilt 4x4x4 block with
 // sixteen 128-bit stores.  The only barrier is the one after the table copy.
-__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+__global__ void __launch_bounds__(kThreads, kDecCtasPerSm)
 zfp_decode_slab_kernel(const uint32_t* __restrict__ in, float* __restrict__ out, uint32_t nz, int maxbits) {
   extern __shared__ __align__(16) uint32_t smem_words[];
   const int nwords = maxbits >> 5;
