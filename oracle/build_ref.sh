@@ -1,6 +1,6 @@
 #!/bin/sh
 # Builds oracle/_ref/libcswap_ref.so from the reference's own sources where
-# they lie (default /root/reference).  Nothing from the reference is copied
+# they lie (CSWAP_REFERENCE names the checkout).  Nothing from the reference is copied
 # into the repository: the two sparse kernels' bodies are cut into a temporary
 # directory for the duration of the compile and removed afterwards.
 # TEST INFRASTRUCTURE ONLY.
