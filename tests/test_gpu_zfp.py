@@ -59,7 +59,7 @@ def test_awkward_blocks_all_word_rates(cs, oracle, maxbits):
     _roundtrip(cs, oracle, a, (32, 32, 40), maxbits)
 
 
-@pytest.mark.parametrize("nz", [1, 2, 3, 5, 15, 16, 17, 18, 19, 31, 33, 67])
+@pytest.mark.parametrize("nz", [1, 2, 3, 5, 7, 8, 9, 12, 15, 16, 17, 18, 19, 31, 33, 67])
 def test_partial_slabs(cs, oracle, nz):
     a = util.tanh_normal(1024 * nz, seed=nz)
     _roundtrip(cs, oracle, a, (32, 32, nz), 512)
