@@ -282,6 +282,12 @@ def run_model_workload(args):
     policy = exe.make_policy(prof, cm, lossy_ids=lossy)
     results["self_tuned"] = W.timed_steps(model, exe, make_batch, steps, warmup)
     counts = {str(k): policy.count(k) for k in (0, 2, 3, 6)}
+    if args.workload == "vgg16":
+        # swap-or-recompute table in the manner of the Capuchin baseline (policy_ 2)
+        exe_cap = fresh(lambda e: None)
+        cap = exe_cap.make_policy_capuchin(prof, cm)
+        results["capuchin_style_baseline"] = W.timed_steps(model, exe_cap, make_batch, steps, warmup)
+        results["capuchin_style_baseline"]["policy_counts"] = {str(k): cap.count(k) for k in (0, 1, 2)}
     # the same decision when loss is acceptable on every float activation
     exe_all = fresh(lambda e: None)
     policy_all = exe_all.make_policy(prof, cm, lossy_ids=[i for i, p in prof.items() if p["float32"]])
@@ -301,7 +307,8 @@ def run_model_workload(args):
             "step_ms": {"no_swap": t_none, "raw_swap": t_raw, "self_tuned": t_tuned,
                         "self_tuned_lossy_everywhere": results["self_tuned_lossy_everywhere"]["ms_per_step"],
                         **{k: results[k]["ms_per_step"]
-                           for k in ("reference_split_zfp8", "vdnn_baseline", "superneurons_baseline")
+                           for k in ("reference_split_zfp8", "vdnn_baseline", "superneurons_baseline",
+                                     "capuchin_style_baseline")
                            if k in results}},
             "peak_device_mib": {k: round(v["peak_device_bytes"] / 2**20, 1) for k, v in results.items()},
             "raw_swap": raw, "self_tuned": tuned,

@@ -284,6 +284,7 @@ class Execution:
                 "start": self._prof_start, "end": ev, "numel": y.numel(), "zero_fraction": zf,
                 "inputs": [getattr(t, "tensor_id", -1) for t in inputs], "omit": isomit,
                 "type": int(layer_type), "float32": y.dtype == torch.float32, "has_grad": y.grad_fn is not None,
+                "recomputable": forward is not None,
             }
             # which consumed tensors autograd holds on to once this consumer has run
             for t in inputs:
@@ -313,24 +314,15 @@ class Execution:
                 "zero_fraction": float(p["zero_fraction"]) if p["zero_fraction"] is not None else -1.0,
                 "inputs": p["inputs"], "omit": p["omit"], "type": p["type"], "float32": p["float32"],
                 "has_grad": p["has_grad"], "saved": self._prof_saved.get(idx, True),
+                "recomputable": p.get("recomputable", False),
             }
         self._prof = {}
         self._prof_saved = {}
         self.profile = False
         return out
 
-    def make_policy(self, prof: Dict[int, dict], cost: CostModel, lossy_ids: Optional[Sequence[int]] = None,
-                    bwd_factor: float = 2.0, min_bytes: int = 1 << 20) -> List[int]:
-        """Fill `policy` / `begin_stage` from a profiled iteration.
-
-        Tensor id i (the output of layer i) becomes a swap candidate at the
-        first layer that consumes it.  The cost model gets, per candidate, the
-        forward time at which that consumer starts and the backward compute
-        that precedes the consumer's backward (taken as `bwd_factor` times the
-        forward time of the layers after it), and simulates the step's link
-        traffic to choose raw / sparse / ZFP.  ZFP is allowed on the ids in
-        `lossy_ids` (default: inputs of CONV layers, which is where the
-        reference's drivers apply it, vgg16-cifar10.cpp:381-397)."""
+    def _candidates(self, prof: Dict[int, dict], lossy_ids, bwd_factor: float, min_bytes: int):
+        """Swap candidates of a profiled iteration with what the cost model needs to know about each."""
         n = max(prof) + 1 if prof else 0
         times = [prof[i]["time_s"] if i in prof else 0.0 for i in range(n)]
         start = [0.0] * (n + 1)
@@ -360,10 +352,60 @@ class Execution:
             cands.append(tid)
             descs.append(TensorDesc(p["numel"], p["zero_fraction"], tid in lossy, ready_s=start[c],
                                     need_s=bwd_factor * (fwd_total - start[c + 1])))
+        return n, fwd_total, consumer, cands, descs
+
+    def make_policy(self, prof: Dict[int, dict], cost: CostModel, lossy_ids: Optional[Sequence[int]] = None,
+                    bwd_factor: float = 2.0, min_bytes: int = 1 << 20) -> List[int]:
+        """Fill `policy` / `begin_stage` from a profiled iteration.
+
+        Tensor id i (the output of layer i) becomes a swap candidate at the
+        first layer that consumes it.  The cost model gets, per candidate, the
+        forward time at which that consumer starts and the backward compute
+        that precedes the consumer's backward (taken as `bwd_factor` times the
+        forward time of the layers after it), and simulates the step's link
+        traffic to choose raw / sparse / ZFP.  ZFP is allowed on the ids in
+        `lossy_ids` (default: inputs of CONV layers, which is where the
+        reference's drivers apply it, vgg16-cifar10.cpp:381-397)."""
+        n, fwd_total, consumer, cands, descs = self._candidates(prof, lossy_ids, bwd_factor, min_bytes)
         pol, _ = cost.decide(descs, fwd_total)
         for tid in range(n):
             self.policy[tid] = POLICY_KEEP
         for tid, pcode in zip(cands, pol):
             self.policy[tid] = pcode
             self.begin_stage[tid] = consumer[tid]
+        return list(self.policy)
+
+    def make_policy_capuchin(self, prof: Dict[int, dict], cost: CostModel, bwd_factor: float = 2.0,
+                             min_bytes: int = 1 << 20) -> List[int]:
+        """A swap-or-recompute table in the manner of the Capuchin baseline
+        (`policy_` 2; the reference takes its table from the fork's
+        PolicyMaker::capuchin, vgg16-style drivers at Desnet-cifar10.cpp:723-731,
+        which is not part of the tree).  Every candidate starts as a raw swap;
+        the step is simulated on the measured link, and while some tensor's
+        modelled stall exceeds the forward time of the layer that produced it,
+        the worst such tensor is dropped and rebuilt instead (policy 1) and the
+        simulation repeated.  Only tensors whose producer was passed to `post`
+        during the profiled iteration can be rebuilt."""
+        n, fwd_total, consumer, cands, descs = self._candidates(prof, [], bwd_factor, min_bytes)
+        for d in descs:
+            d.zero_fraction = -1.0  # no codec: Capuchin moves tensors as they are
+        active = list(range(len(cands)))
+        dropped = set()
+        while active:
+            _, stall = cost.decide([descs[i] for i in active], fwd_total)
+            best, gain = -1, 0.0
+            for j, i in enumerate(active):
+                p = prof[cands[i]]
+                if p.get("recomputable") and stall[j] - p["time_s"] > gain:
+                    best, gain = i, stall[j] - p["time_s"]
+            if best < 0:
+                break
+            dropped.add(best)
+            active.remove(best)
+        for tid in range(n):
+            self.policy[tid] = POLICY_KEEP
+        for i, tid in enumerate(cands):
+            self.policy[tid] = POLICY_DROP if i in dropped else POLICY_RAW
+            self.begin_stage[tid] = consumer[tid]
+        self.policy_ = 2
         return list(self.policy)

@@ -427,15 +427,26 @@ def test_profile_and_make_policy(cs):
         lt = cs.LayerType.CONV if isinstance(layer, torch.nn.Conv2d) else cs.LayerType.ACT
         exe.pre(h, lt)
         out = layer(h)
-        exe.post(h, out, lt)
+        exe.post(h, out, lt, False, layer)
         h = out
     exe.postforward()
     prof = exe.finish_profile()
     assert len(prof) == len(net) and all(p["time_s"] >= 0 for p in prof.values())
+    assert not prof[0]["saved"] and prof[1]["saved"]  # conv output feeds a ReLU; the ReLU output is kept
     assert 0.3 < prof[1]["zero_fraction"] < 0.7  # first ReLU output
     cm = cs.CostModel.fit(exe.mgr)
     pol = exe.make_policy(prof, cm, min_bytes=1 << 16)
     assert len(pol) >= len(net)
     assert set(pol) <= {0, 2, 3, 6}
     assert exe.begin_stage[1] == 2  # ReLU output is consumed by the next conv
+    assert pol[0] == 0               # nothing keeps the first conv's output: not a candidate
+    # swap-or-recompute table in the manner of Capuchin: raw swaps and rebuilds only, planner code 2
+    cap = exe.make_policy_capuchin(prof, cm, min_bytes=1 << 16)
+    assert set(cap) <= {0, 1, 2} and exe.policy_ == 2 and cap[1] in (1, 2) and cap[0] == 0
+    # a link a thousand times slower makes every copy stall: everything that can be rebuilt is
+    slow = cs.CostModel.fit(exe.mgr)
+    slow.c.d2h_bps /= 1000.0
+    slow.c.h2d_bps /= 1000.0
+    cap_slow = exe.make_policy_capuchin(prof, slow, min_bytes=1 << 16)
+    assert cap_slow.count(1) > cap.count(1) and cap_slow.count(1) >= 2
     exe.mgr.close()
