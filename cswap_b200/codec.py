@@ -17,7 +17,15 @@ from ._lib import SparseLayout, check, lib
 POLICY_KEEP, POLICY_DROP, POLICY_RAW, POLICY_SPARSE, POLICY_ZFP = 0, 1, 2, 3, 6
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream_ptr(device) -> int:
+    """cudaStream_t of torch's current stream on `device` (the raw accessor
+    skips building a Stream object, which matters at one call per swapped tensor)."""
+    if _raw_stream is not None:
+        dev = torch.device(device) if not isinstance(device, torch.device) else device
+        return _raw_stream(dev.index if dev.index is not None else torch.cuda.current_device())
     return torch.cuda.current_stream(device).cuda_stream
 
 

@@ -169,33 +169,43 @@ class Execution:
         self._produced.clear()
 
     # ---- saved-tensor hooks ------------------------------------------------------
-    def _eligible(self, t: torch.Tensor) -> bool:
-        return (t.is_cuda and t.dtype == torch.float32 and t.numel() >= self.min_numel and t.is_contiguous()
-                and not (t.is_leaf and t.requires_grad)
-                and t.untyped_storage().nbytes() == t.numel() * 4 and t.storage_offset() == 0)
+    def _key(self, t: torch.Tensor) -> Optional[int]:
+        """Address of t's storage when t is a whole, contiguous float32 CUDA
+        storage worth tracking, else None (one storage lookup for both answers)."""
+        if not (t.is_cuda and t.dtype == torch.float32 and t.numel() >= self.min_numel and t.is_contiguous()
+                and t.storage_offset() == 0) or (t.is_leaf and t.requires_grad):
+            return None
+        st = t.untyped_storage()
+        return st.data_ptr() if st.nbytes() == t.numel() * 4 else None
 
-    def _record_for(self, t: torch.Tensor) -> _Record:
-        key = t.untyped_storage().data_ptr()
+    def _eligible(self, t: torch.Tensor) -> bool:
+        return self._key(t) is not None
+
+    def _record_for(self, t: torch.Tensor, key: Optional[int] = None) -> _Record:
+        if key is None:
+            key = t.untyped_storage().data_ptr()
         rec = self._records.get(key)
-        if rec is None or rec.tensor is None or rec.tensor.untyped_storage().data_ptr() != key \
-                or rec.numel != t.numel():
+        if rec is None or rec.tensor is None or rec.numel != t.numel() \
+                or rec.tensor.untyped_storage().data_ptr() != key:
             rec = _Record(t.detach().view(-1), self)
             self._records[key] = rec
         return rec
 
     def _pack(self, t: torch.Tensor):
-        if not self._eligible(t):
+        key = self._key(t)
+        if key is None:
             return t
-        rec = self._record_for(t)
+        rec = self._record_for(t, key)
         rec.saved = True
-        return _Packed(rec, t.shape, t.stride(), t.storage_offset())
+        return _Packed(rec, t.shape, t.stride(), 0)
 
     def _ref(self, t: torch.Tensor):
         """Like _pack, for the producer notes: a way back to the tensor that does
         not count as autograd having saved it."""
-        if not self._eligible(t):
+        key = self._key(t)
+        if key is None:
             return t
-        return _Packed(self._record_for(t), t.shape, t.stride(), t.storage_offset())
+        return _Packed(self._record_for(t, key), t.shape, t.stride(), 0)
 
     def _unpack(self, p):
         if not isinstance(p, _Packed):
@@ -229,9 +239,12 @@ class Execution:
             if tid < 0 or tid >= len(self.begin_stage) or self.index != self.begin_stage[tid] or t.grad_fn is None:
                 continue
             pol = self._effective_policy(tid, layer_type)
-            if pol not in (POLICY_DROP, POLICY_RAW, POLICY_SPARSE, POLICY_ZFP) or not self._eligible(t):
+            if pol not in (POLICY_DROP, POLICY_RAW, POLICY_SPARSE, POLICY_ZFP):
                 continue
-            rec = self._record_for(t)
+            key = self._key(t)
+            if key is None:
+                continue
+            rec = self._record_for(t, key)
             if rec.ticket is not None or rec.dropped:
                 continue
             if pol == POLICY_DROP:
