@@ -230,7 +230,7 @@ csw_status csw_cost_decide(const csw_cost_model* cm, const csw_tensor_desc* td, 
     sparse[i] = {CSW_POLICY_SPARSE, cm->sparse_enc_a + cm->sparse_enc_b * b, cm->sparse_dec_a + cm->sparse_dec_b * b,
                  b * (1.0 - (zf < 0 ? 0 : zf)) + b / 32.0 + (double)td[i].numel / 1024.0, zf >= 0};
     zfp[i] = {CSW_POLICY_ZFP, cm->zfp_enc_a + cm->zfp_enc_b * b, cm->zfp_dec_a + cm->zfp_dec_b * b, b * rate / 32.0,
-              td[i].lossy_ok && td[i].numel % 1024 == 0 && td[i].numel > 0};
+              td[i].lossy_ok && td[i].numel >= 1024};
     cur[i] = raw[i];
     order[i] = i;
   }

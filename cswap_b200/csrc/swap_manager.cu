@@ -275,11 +275,16 @@ void* pool_alloc(csw_mgr* m, Pool& pool, size_t bytes, size_t* got) {
   return p;
 }
 
-csw_status zfp_geometry(size_t numel, unsigned maxbits, size_t* nz, size_t* bytes) {
-  size_t nx, ny;
-  csw_status st = csw_zfp_view(numel, &nx, &ny, nz);
+// A tensor under policy 6 travels as the ZFP stream of its first nz 32x32
+// slabs followed by the numel % 1024 values that do not fill a slab, as they
+// are.  `bytes` is the whole payload, `zbytes` the stream alone.
+csw_status zfp_geometry(size_t numel, unsigned maxbits, size_t* nz, size_t* zbytes, size_t* bytes) {
+  *nz = numel / 1024;
+  if (*nz == 0) return CSW_ERR_UNSUPPORTED;  // less than one slab: not worth a codec launch
+  csw_status st = csw_zfp_max_bytes(32, 32, *nz, maxbits, zbytes);
   if (st != CSW_OK) return st;
-  return csw_zfp_max_bytes(32, 32, *nz, maxbits, bytes);
+  *bytes = *zbytes + (numel % 1024) * sizeof(float);
+  return CSW_OK;
 }
 
 }  // namespace
@@ -365,8 +370,9 @@ csw_status csw_swap_out(csw_mgr* m, const float* d_ptr, size_t numel, int policy
   if (!g.ok) return CSW_ERR_ARG;
   poll(m);
 
-  size_t nz = 0, zbytes = 0;
-  if (policy == CSW_POLICY_ZFP && zfp_geometry(numel, m->maxbits, &nz, &zbytes) != CSW_OK) policy = CSW_POLICY_RAW;
+  size_t nz = 0, zstream = 0, zbytes = 0;  // slabs, stream bytes, stream + raw tail
+  if (policy == CSW_POLICY_ZFP && zfp_geometry(numel, m->maxbits, &nz, &zstream, &zbytes) != CSW_OK)
+    policy = CSW_POLICY_RAW;
   csw_sparse_layout L{};
   if (policy == CSW_POLICY_SPARSE && (csw_sparse_layout_of(numel, &L) != CSW_OK || m->free_slots.empty()))
     policy = CSW_POLICY_RAW;
@@ -418,7 +424,10 @@ csw_status csw_swap_out(csw_mgr* m, const float* d_ptr, size_t numel, int policy
     t->moved_final = true;
   } else if (policy == CSW_POLICY_ZFP) {
     st = csw_zfp_compress(d_ptr, 32, 32, nz, m->maxbits, t->stage, t->stage_cap, nullptr, m->s_codec);
-    if (st == CSW_OK) {
+    if (st == CSW_OK && zbytes > zstream)  // the values past the last whole slab
+      e = cudaMemcpyAsync(static_cast<char*>(t->stage) + zstream, d_ptr + nz * 1024, zbytes - zstream,
+                          cudaMemcpyDeviceToDevice, m->s_codec);
+    if (st == CSW_OK && e == cudaSuccess) {
       e = cudaEventRecord(t->ev_read, m->s_codec);
       if (e == cudaSuccess) e = cudaStreamWaitEvent(m->s_d2h, t->ev_read, 0);
       if (e == cudaSuccess) e = cudaMemcpyAsync(t->host, t->stage, zbytes, cudaMemcpyDeviceToHost, m->s_d2h);
@@ -571,10 +580,17 @@ csw_status csw_swap_in(csw_mgr* m, csw_ticket* t, float* d_dst, csw_stream_t com
     if (st != CSW_OK) return st;
     e = cudaStreamWaitEvent(m->s_codec, t->ev_h2d, 0);
     if (e != cudaSuccess) return cuda_fail(e);
-    if (t->policy == CSW_POLICY_ZFP)
-      st = csw_zfp_decompress(t->stage, t->moved, 32, 32, t->numel / 1024, t->maxbits, d_dst, m->s_codec);
-    else
+    if (t->policy == CSW_POLICY_ZFP) {
+      const size_t nz = t->numel / 1024, tail = (t->numel % 1024) * sizeof(float);
+      st = csw_zfp_decompress(t->stage, t->moved - tail, 32, 32, nz, t->maxbits, d_dst, m->s_codec);
+      if (st == CSW_OK && tail) {
+        e = cudaMemcpyAsync(d_dst + nz * 1024, static_cast<const char*>(t->stage) + (t->moved - tail), tail,
+                            cudaMemcpyDeviceToDevice, m->s_codec);
+        if (e != cudaSuccess) return cuda_fail(e);
+      }
+    } else {
       st = csw_sparse_decompress(t->stage, t->numel, d_dst, m->s_codec);
+    }
     if (st != CSW_OK) return st;
     e = cudaEventRecord(t->ev_done, m->s_codec);
   }
@@ -637,8 +653,9 @@ csw_status csw_blob_info(const void* blob, size_t bytes, csw_blob_header* header
   if (h.policy == CSW_POLICY_RAW) {
     if (h.payload_bytes != h.numel * sizeof(float) || h.nnz != 0 || h.zfp_maxbits != 0) return CSW_ERR_ARG;
   } else if (h.policy == CSW_POLICY_ZFP) {
-    size_t nz = 0, zbytes = 0;
-    if (zfp_geometry(h.numel, h.zfp_maxbits, &nz, &zbytes) != CSW_OK || h.payload_bytes != zbytes || h.nnz != 0)
+    size_t nz = 0, zstream = 0, zbytes = 0;
+    if (zfp_geometry(h.numel, h.zfp_maxbits, &nz, &zstream, &zbytes) != CSW_OK || h.payload_bytes != zbytes ||
+        h.nnz != 0)
       return CSW_ERR_ARG;
   } else if (h.policy == CSW_POLICY_SPARSE) {
     csw_sparse_layout L;

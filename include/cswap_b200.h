@@ -94,7 +94,8 @@ csw_status csw_zfp_decompress_strided(const void* d_in, size_t bytes, size_t nx,
 
 /* The swap path's view of a flat tensor (BASELINE: nx = ny = 32,
  * nz = numel / 1024).  Returns CSW_ERR_UNSUPPORTED when numel is not a
- * multiple of 1024 (such tensors are swapped raw). */
+ * multiple of 1024 (the swap manager then codes the whole slabs and moves the
+ * remaining numel % 1024 values as they are). */
 csw_status csw_zfp_view(size_t numel, size_t* nx, size_t* ny, size_t* nz);
 
 /* ---- 3. sparse zero-value codec ------------------------------------------ */
@@ -197,8 +198,10 @@ csw_status csw_mgr_get_streams(csw_mgr* m, csw_stream_t* codec, csw_stream_t* d2
  * on the manager's D2H stream.  Returns immediately; *ticket identifies the
  * host copy.  The caller may release d_ptr once csw_swap_out_done() reports
  * completion or after making its own stream wait with csw_swap_out_wait().
- * A policy whose codec does not apply to `numel` (ZFP needs numel % 1024 == 0)
- * falls back to CSW_POLICY_RAW; the ticket records what was used. */
+ * Under CSW_POLICY_ZFP the first numel / 1024 slabs of 32x32 values are coded
+ * and the rest (numel % 1024 values) travels uncoded behind the stream; a
+ * tensor of fewer than 1024 values falls back to CSW_POLICY_RAW.  The ticket
+ * records what was used. */
 csw_status csw_swap_out(csw_mgr* m, const float* d_ptr, size_t numel, int policy, csw_stream_t compute,
                         csw_ticket** ticket);
 /* 1 in *done when the tensor's device bytes are no longer needed. */

@@ -65,13 +65,14 @@ def test_cost_decision_is_pure_host_logic(L):
         cs.TensorDesc(n, 0.0, True, ready_s=3e-4, need_s=1.4e-3),     # dense, loss allowed
         cs.TensorDesc(n, 0.0, False, ready_s=5e-4, need_s=1.0e-3),    # dense, lossless: nothing applies
         cs.TensorDesc(n, -1.0, False, ready_s=7e-4, need_s=0.6e-3),   # sparsity unknown, lossless
-        cs.TensorDesc(n + 8, 0.0, True, ready_s=9e-4, need_s=0.2e-3),  # not a multiple of 1024: no ZFP
+        cs.TensorDesc(n + 8, 0.0, True, ready_s=9e-4, need_s=0.2e-3),  # not a multiple of 1024: ZFP + raw tail
+        cs.TensorDesc(1000, 0.0, True, ready_s=9.5e-4, need_s=0.1e-3),  # less than one 32x32 slab: no ZFP
     ]
     pol, stall = cm.decide(tensors, fwd)
-    assert pol == [3, 6, 2, 2, 2]
+    assert pol == [3, 6, 2, 2, 6, 2]
     all_raw = [cs.TensorDesc(t.numel, -1.0, False, t.ready_s, t.need_s) for t in tensors]
     pol_raw, stall_raw = cm.decide(all_raw, fwd)
-    assert pol_raw == [2] * 5 and sum(stall) < 0.75 * sum(stall_raw)
+    assert pol_raw == [2] * 6 and sum(stall) < 0.75 * sum(stall_raw)
     # when the link keeps up with compute nothing stalls and nothing is compressed
     small = [cs.TensorDesc(1 << 18, 0.9, True, ready_s=1e-4 * i, need_s=1e-3 * (5 - i)) for i in range(5)]
     pol2, stall2 = cm.decide(small, 1e-3)
@@ -124,8 +125,11 @@ def test_blob_header_validation_without_a_device(L):
         cs.blob_info(raw[:-1])                               # payload cut short
     # zfp: 4096 values = 32x32x4 = 64 blocks of 512 bits
     assert cs.blob_info(blob(6, 4096, bytes(4096), maxbits=512))["zfp_maxbits"] == 512
+    assert cs.blob_info(blob(6, 4096 + 5, bytes(4096 + 20), maxbits=512))["numel"] == 4101  # stream + raw tail
     with pytest.raises(cs.CswapError):
-        cs.blob_info(blob(6, 4000, bytes(4096), maxbits=512))  # not a whole number of 32x32 slabs
+        cs.blob_info(blob(6, 4096 + 5, bytes(4096), maxbits=512))  # the tail is missing
+    with pytest.raises(cs.CswapError):
+        cs.blob_info(blob(6, 1000, bytes(4000), maxbits=512))      # less than one slab never travels as ZFP
     with pytest.raises(cs.CswapError):
         cs.blob_info(blob(6, 4096, bytes(2048), maxbits=512))
     # sparse: 5000 elements, two tiles, non-zeros at 3, 40 and 4100

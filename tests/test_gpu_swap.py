@@ -152,13 +152,31 @@ def test_sparse_exact_and_sized(cs, mgr):
     assert mgr.stats()["pinned_in_use"] == 0
 
 
-def test_zfp_falls_back_to_raw_for_odd_sizes(cs, mgr):
+def test_zfp_odd_sizes(cs, mgr):
+    """Less than one 32x32 slab: raw.  Otherwise the whole slabs go through the
+    codec and the values past the last slab travel as they are."""
     import torch
     t = torch.from_numpy(util.normal(1000, 4)).cuda()
     tk = mgr.swap_out(t, cs.POLICY_ZFP)
     assert tk.info()["policy"] == cs.POLICY_RAW
     assert torch.equal(mgr.swap_in(tk), t)
     tk.release()
+    for n in (1024 + 1, 5 * 1024 + 777, 300 * 1024 + 1023):
+        t = torch.tanh(torch.from_numpy(util.normal(n, n)).cuda())
+        whole = n // 1024 * 1024
+        tk = mgr.swap_out(t, cs.POLICY_ZFP)
+        info = tk.info()
+        assert info["policy"] == cs.POLICY_ZFP
+        assert info["moved_bytes"] == cs.zfp_max_bytes(32, 32, n // 1024, 512) + 4 * (n - whole)
+        back = mgr.swap_in(tk)
+        torch.cuda.synchronize()
+        want = cs.zfp_decompress(cs.zfp_compress(t[:whole].contiguous(), 512), whole, 512)
+        assert torch.equal(back[:whole], want) and torch.equal(back[whole:], t[whole:])
+        blob = tk.export()
+        tk.release()
+        tk2 = mgr.import_blob(blob)
+        assert torch.equal(mgr.swap_in(tk2), back)
+        tk2.release()
 
 
 def test_many_tensors_interleaved_with_compute(cs, mgr):
