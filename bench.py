@@ -210,6 +210,20 @@ def workload_config(args):
             "parallelism": f"{args.gpus} independent replica(s), no collective"}
 
 
+def bind_host_threads_near_gpu(index: int) -> bool:
+    """Run this process on the CPUs next to its GPU (NVML's affinity for the
+    device), so that the pinned host buffers it allocates land in the memory
+    of that socket.  With several ranks per host the end-to-end numbers
+    otherwise share one socket's memory.  A property of this process only."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        pynvml.nvmlDeviceSetCpuAffinity(pynvml.nvmlDeviceGetHandleByIndex(index))
+        return True
+    except Exception:
+        return False
+
+
 def run_model_workload(args):
     """Swapped training step (VGG16 batch 128 on 3x32x32, or BERT-base-shaped
     encoder batch 32 x seq 512): step latency without swapping, with raw swap of
@@ -346,6 +360,8 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the codec has no CPU path")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    if world > 1:
+        bind_host_threads_near_gpu(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     L = cs.lib()
