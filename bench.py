@@ -275,6 +275,13 @@ def run_model_workload(args):
     results = {}
     results["no_swap"] = W.timed_steps(model, fresh(lambda e: None), make_batch, steps, warmup)
     results["raw_swap"] = W.timed_steps(model, fresh(all_raw), make_batch, steps, warmup)
+
+    def all_zfp(exe):
+        for i in range(nids):
+            exe.begin_stage[i] = i + 1
+            exe.policy[i] = cs.POLICY_ZFP
+
+    results["zfp_everywhere"] = W.timed_steps(model, fresh(all_zfp), make_batch, steps, warmup)
     if args.workload == "vgg16":
         results["reference_split_zfp8"] = W.timed_steps(model, fresh(W.vgg16_reference_policy), make_batch, steps,
                                                         warmup)
@@ -292,10 +299,20 @@ def run_model_workload(args):
     model.forward_with(exe, x, y).backward()
     prof = exe.finish_profile()
     cm = cs.CostModel.fit(mgr, maxbits)
+    def run_under(e):
+        def run(k):
+            r = W.timed_steps(model, e, make_batch, k, 0)
+            return r["ms_per_step"] * k * 1e-3
+        return run
+
+    # the cost model's table, then a short measured run-off against its ZFP-eager neighbour
     lossy = None if args.workload == "vgg16" else [i for i, p in prof.items() if p["float32"]]
-    policy = exe.make_policy(prof, cm, lossy_ids=lossy)
+    cands = exe.policy_candidates(prof, cm, lossy_ids=lossy)
+    chosen = exe.refine_policy(cands, run_under(exe))
+    policy = list(exe.policy)
     results["self_tuned"] = W.timed_steps(model, exe, make_batch, steps, warmup)
     counts = {str(k): policy.count(k) for k in (0, 2, 3, 6)}
+    counts["chosen"] = chosen
     if args.workload == "vgg16":
         # swap-or-recompute table in the manner of the Capuchin baseline (policy_ 2)
         exe_cap = fresh(lambda e: None)
@@ -304,9 +321,12 @@ def run_model_workload(args):
         results["capuchin_style_baseline"]["policy_counts"] = {str(k): cap.count(k) for k in (0, 1, 2)}
     # the same decision when loss is acceptable on every float activation
     exe_all = fresh(lambda e: None)
-    policy_all = exe_all.make_policy(prof, cm, lossy_ids=[i for i, p in prof.items() if p["float32"]])
+    cands_all = exe_all.policy_candidates(prof, cm, lossy_ids=[i for i, p in prof.items() if p["float32"]])
+    chosen_all = exe_all.refine_policy(cands_all, run_under(exe_all))
+    policy_all = list(exe_all.policy)
     results["self_tuned_lossy_everywhere"] = W.timed_steps(model, exe_all, make_batch, steps, warmup)
     counts_all = {str(k): policy_all.count(k) for k in (0, 2, 3, 6)}
+    counts_all["chosen"] = chosen_all
     t_tuned, t_raw, t_none = (max_over_ranks([results[k]["ms_per_step"]], dev)[0]
                               for k in ("self_tuned", "raw_swap", "no_swap"))
     raw, tuned = results["raw_swap"], results["self_tuned"]
@@ -321,17 +341,14 @@ def run_model_workload(args):
             "step_ms": {"no_swap": t_none, "raw_swap": t_raw, "self_tuned": t_tuned,
                         "self_tuned_lossy_everywhere": results["self_tuned_lossy_everywhere"]["ms_per_step"],
                         **{k: results[k]["ms_per_step"]
-                           for k in ("reference_split_zfp8", "vdnn_baseline", "superneurons_baseline",
-                                     "capuchin_style_baseline")
+                           for k in ("zfp_everywhere", "reference_split_zfp8", "vdnn_baseline",
+                                     "superneurons_baseline", "capuchin_style_baseline")
                            if k in results}},
             "peak_device_mib": {k: round(v["peak_device_bytes"] / 2**20, 1) for k, v in results.items()},
             "raw_swap": raw, "self_tuned": tuned,
             "activation_bytes_per_link_byte": {
-                "raw_swap": raw["activation_bytes_per_step"] / max(raw["link_bytes_out_per_step"], 1),
-                "self_tuned": tuned["activation_bytes_per_step"] / max(tuned["link_bytes_out_per_step"], 1),
-                "self_tuned_lossy_everywhere":
-                    results["self_tuned_lossy_everywhere"]["activation_bytes_per_step"] /
-                    max(results["self_tuned_lossy_everywhere"]["link_bytes_out_per_step"], 1)},
+                k: v["activation_bytes_per_step"] / max(v["link_bytes_out_per_step"], 1)
+                for k, v in results.items() if v["link_bytes_out_per_step"] > 0},
             "cost_model": cm.as_dict(),
         }
         print(json.dumps(line))

@@ -422,3 +422,36 @@ class Execution:
             self.begin_stage[tid] = consumer[tid]
         self.policy_ = 2
         return list(self.policy)
+
+    def policy_candidates(self, prof: Dict[int, dict], cost: CostModel, lossy_ids: Optional[Sequence[int]] = None,
+                          bwd_factor: float = 2.0, min_bytes: int = 1 << 20) -> Dict[str, List[int]]:
+        """The cost model's table and its neighbour with ZFP on every tensor
+        where loss is allowed.  The model minimises the stall it can predict
+        from the profile; on a step that is bound by the host link or by the
+        host itself it predicts too little, and the neighbour is then the
+        faster one.  `refine_policy` settles it by measurement."""
+        model = self.make_policy(prof, cost, lossy_ids, bwd_factor, min_bytes)
+        begin = list(self.begin_stage)
+        _, _, consumer, cands, descs = self._candidates(prof, lossy_ids, bwd_factor, min_bytes)
+        eager = list(model)
+        for tid, d in zip(cands, descs):
+            if d.lossy_ok and d.numel >= 1024:
+                eager[tid] = POLICY_ZFP
+        self.begin_stage = begin
+        return {"model": model, "zfp_where_allowed": eager}
+
+    def refine_policy(self, candidates: Dict[str, List[int]], run_steps, steps: int = 3) -> str:
+        """Install the candidate table that runs fastest: `run_steps(n)` must
+        run n training steps under this Execution and return the seconds they
+        took.  Returns the winner's name.  (One untimed step per candidate
+        first: the pools and the allocator settle on the new traffic.)"""
+        best_name, best_t = None, float("inf")
+        for name, table in candidates.items():
+            self.policy[:len(table)] = table
+            run_steps(1)
+            t = run_steps(steps)
+            if t < best_t:
+                best_name, best_t = name, t
+        self.policy[:len(candidates[best_name])] = candidates[best_name]
+        return best_name
+
