@@ -458,6 +458,16 @@ def test_profile_and_make_policy(cs):
     assert set(pol) <= {0, 2, 3, 6}
     assert exe.begin_stage[1] == 2  # ReLU output is consumed by the next conv
     assert pol[0] == 0               # nothing keeps the first conv's output: not a candidate
+    # the model's table and its ZFP-eager neighbour; the run-off installs whichever "runs" faster
+    cands = exe.policy_candidates(prof, cm, lossy_ids=[1, 3, 4, 6], min_bytes=1 << 16)
+    assert set(cands) == {"model", "zfp_where_allowed"} and cands["model"][1] in (2, 3, 6)
+    assert all(cands["zfp_where_allowed"][i] == 6 for i in (1, 3, 4, 6))
+    fake = iter([0.0, 3.0, 0.0, 2.0])       # seconds returned for (settle, timed) x (model, neighbour)
+    assert exe.refine_policy(cands, lambda k: next(fake)) == "zfp_where_allowed"
+    assert exe.policy[:len(net)] == cands["zfp_where_allowed"][:len(net)]
+    fake = iter([0.0, 1.0, 0.0, 2.0])
+    assert exe.refine_policy(cands, lambda k: next(fake)) == "model"
+    assert exe.policy[:len(net)] == cands["model"][:len(net)]
     # swap-or-recompute table in the manner of Capuchin: raw swaps and rebuilds only, planner code 2
     cap = exe.make_policy_capuchin(prof, cm, min_bytes=1 << 16)
     assert set(cap) <= {0, 1, 2} and exe.policy_ == 2 and cap[1] in (1, 2) and cap[0] == 0
