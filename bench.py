@@ -511,7 +511,7 @@ def main():
 def side_measurements(cs, torch, dev, peak):
     """Sparse codec throughput per sparsity (16 MiB and 256 MiB tensors) and the
     swap manager's host-link numbers.  Reported beside the headline, not in it."""
-    out = {"sparse": [], "swap": {}}
+    out = {"sparse": [], "swap": {}, "zfp_rates": []}
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
     def timeit(fn, reps=10):
@@ -549,6 +549,20 @@ def side_measurements(cs, torch, dev, peak):
                 "decompress_frac_hbm": alg / td / 1e9 / peak,
                 "exact": bool(torch.equal(back.view(torch.int32), t.view(torch.int32)))})
             del t, packed, back
+    # the ZFP kernels at the other two rates the reference's drivers use (256 MiB tensor)
+    n = 256 * 262144
+    t = torch.tanh(torch.randn(n, device=dev))
+    back = torch.empty_like(t)
+    for rate in (4, 8, 16):
+        mb = 64 * rate
+        comp = torch.empty(cs.zfp_max_bytes(32, 32, n // 1024, mb), dtype=torch.uint8, device=dev)
+        te = timeit(lambda: cs.zfp_compress(t, mb, out=comp))
+        td = timeit(lambda: cs.zfp_decompress(comp, n, mb, out=back))
+        alg = 4 * n + n * rate // 8
+        out["zfp_rates"].append({"tensor_mib": 256, "rate": rate, "encode_ms": te * 1e3, "decode_ms": td * 1e3,
+                                 "encode_frac_hbm": alg / te / 1e9 / peak, "decode_frac_hbm": alg / td / 1e9 / peak})
+        del comp
+    del t, back
     # swap link: raw vs ZFP-8 swap-out + swap-in of a 64 MiB tensor through the manager
     mgr = cs.SwapManager(pinned_bytes=512 << 20, staging_bytes=256 << 20)
     n = 64 * 262144
