@@ -6,13 +6,13 @@
 //
 //  * slab kernels for the swap path's view (nx = ny = 32, contiguous, whole
 //    32-bit words per block): one CTA per group of 8 z-slabs (32 KiB, 128
-//    blocks), four (encoder) or five (decoder) CTAs per SM, lane = zfp block held
-//    in registers.  A lane moves its block with
-//    sixteen 128-bit accesses (eight neighbouring lanes cover one 128-byte row
-//    segment, so a warp access touches four whole lines); stream words sit
-//    word-major in shared memory (bank = lane, so diverged lanes never
-//    conflict) and each lane reads or writes its own 128-bit pieces of the
-//    stream.  After the lookup table is in place no warp waits for another.
+//    blocks), four (encoder) or five (decoder) CTAs per SM, lane = zfp block
+//    held in registers.  A lane moves its block with sixteen 128-bit accesses
+//    (eight neighbouring lanes cover one 128-byte row segment, so a warp
+//    access touches four whole lines); stream words sit word-major in shared
+//    memory (bank = lane, so diverged lanes never conflict) and each lane
+//    reads or writes its own 128-bit pieces of the stream.  After the lookup
+//    table is in place no warp waits for another.
 //    Measured against a persistent variant that pulled each group with a bulk
 //    async copy into a shared tile and wrote the stream through a transposing
 //    copy-out: the extra shared-memory hop, its barriers and the registers of
