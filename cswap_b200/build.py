@@ -53,14 +53,6 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
-def build_probe() -> str:
-    """Compile csrc/pipe_probe.cu, the instruction-throughput diagnostic behind the ZFP kernels' design."""
-    exe = os.path.join(HERE, "pipe_probe")
-    subprocess.check_call([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17",
-                           os.path.join(CSRC, "pipe_probe.cu"), "-o", exe])
-    return exe
-
-
 def build_cpp_driver(force: bool = False) -> str:
     """Compile tests/cpp/execution_driver.cpp (the C++ Execution class over stock
     libtorch) against the in-tree library with g++."""
@@ -85,7 +77,4 @@ def build_cpp_driver(force: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    if "--probe" in sys.argv:
-        print(build_probe())
-        sys.exit(0)
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -303,6 +303,12 @@ cudaError_t zfp_encode_launch(const FieldGeom& g, const float* in, void* out, in
   if (maxbits & 31) {
     cudaError_t e = cudaMemsetAsync(out, 0, stream_bytes(g, (unsigned)maxbits), stream);
     if (e != cudaSuccess) return e;
+  } else if ((nblocks * (uint64_t)maxbits) & 63) {
+    // whole 32-bit words per block but an odd number of them in total: the
+    // stream is sized in 64-bit words, so its last 32 bits belong to no block
+    const size_t nbytes = stream_bytes(g, (unsigned)maxbits);
+    cudaError_t e = cudaMemsetAsync(static_cast<char*>(out) + nbytes - 8, 0, 8, stream);
+    if (e != cudaSuccess) return e;
   }
   const unsigned grid = (unsigned)((nblocks + 127) / 128);
   uint32_t* o = reinterpret_cast<uint32_t*>(out);

@@ -5,7 +5,8 @@
 # directory for the duration of the compile and removed afterwards.
 # TEST INFRASTRUCTURE ONLY.
 set -e
-REF="${CSWAP_REFERENCE:-/root/reference}/CSWAP+/zfp"
+[ -n "$CSWAP_REFERENCE" ] || { echo "set CSWAP_REFERENCE to the reference checkout" >&2; exit 3; }
+REF="$CSWAP_REFERENCE/CSWAP+/zfp"
 HERE="$(cd "$(dirname "$0")" && pwd)"
 OUT="$HERE/_ref"
 CUDA_INC="${CUDA_HOME:-/usr/local/cuda}/include"

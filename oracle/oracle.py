@@ -10,6 +10,14 @@ Two shared objects are wrapped:
 * ``_ref/libcswap_ref.so`` - the reference's own headers compiled for the host
   (``ref_shim.cpp`` + ``build_ref.sh``); only buildable where the reference
   tree is mounted, used to pin the restatement and to generate fixtures.
+* ``_ref/libcswap_ref_cuda.so`` - the reference's own CUDA codec compiled for
+  sm_100a (``ref_cuda_shim.cpp`` + ``build_ref_cuda.sh``); built where the
+  reference tree is mounted, runs wherever a GPU is: the GPU tests compare the
+  product's streams with it and the bench times it as the reference arm.
+
+The reference checkout is found through the environment variable
+``CSWAP_REFERENCE`` or, failing that, as a directory named ``reference`` next
+to this repository.
 """
 from __future__ import annotations
 
@@ -22,6 +30,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _ORACLE_SO = os.path.join(_HERE, "libcswap_oracle.so")
 _REF_SO = os.path.join(_HERE, "_ref", "libcswap_ref.so")
+_REF_CUDA_SO = os.path.join(_HERE, "_ref", "libcswap_ref_cuda.so")
 
 TILE = 4096
 
@@ -32,11 +41,26 @@ def build(force: bool = False) -> None:
     src = os.path.join(_HERE, "cswap_oracle.c")
     if force or not os.path.exists(_ORACLE_SO) or os.path.getmtime(_ORACLE_SO) < os.path.getmtime(src):
         subprocess.check_call(["make", "-C", _HERE, "-s", "-B", "libcswap_oracle.so"])
-    ref_root = os.environ.get("CSWAP_REFERENCE", "/root/reference")
-    if os.path.isdir(os.path.join(ref_root, "CSWAP+", "zfp")):
+    ref_root = reference_root()
+    if ref_root is not None:
+        env = dict(os.environ, CSWAP_REFERENCE=ref_root)
         shim = os.path.join(_HERE, "ref_shim.cpp")
         if force or not os.path.exists(_REF_SO) or os.path.getmtime(_REF_SO) < os.path.getmtime(shim):
-            subprocess.check_call([os.path.join(_HERE, "build_ref.sh")], stdout=subprocess.DEVNULL)
+            subprocess.check_call([os.path.join(_HERE, "build_ref.sh")], stdout=subprocess.DEVNULL, env=env)
+        shim = os.path.join(_HERE, "ref_cuda_shim.cpp")
+        if force or not os.path.exists(_REF_CUDA_SO) or os.path.getmtime(_REF_CUDA_SO) < os.path.getmtime(shim):
+            subprocess.check_call([os.path.join(_HERE, "build_ref_cuda.sh")], stdout=subprocess.DEVNULL,
+                                  stderr=subprocess.DEVNULL, env=env)
+
+
+def reference_root():
+    """Directory of the reference checkout, or None where it is not mounted."""
+    cands = [os.environ.get("CSWAP_REFERENCE"),
+             os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")]
+    for c in cands:
+        if c and os.path.isdir(os.path.join(c, "CSWAP+", "zfp")):
+            return os.path.abspath(c)
+    return None
 
 
 _lib = None
@@ -126,6 +150,37 @@ def ref():
                                             C.POINTER(C.c_uint32), C.POINTER(C.c_int32)]
         _ref = R
     return _ref
+
+
+def have_ref_cuda() -> bool:
+    return os.path.exists(_REF_CUDA_SO)
+
+
+_ref_cuda = None
+
+
+def ref_cuda():
+    """The reference's CUDA codec (needs a GPU).  Arguments are raw device
+    pointers; every call runs on the legacy default stream and blocks."""
+    global _ref_cuda
+    if _ref_cuda is None:
+        R = C.CDLL(_REF_CUDA_SO, mode=os.RTLD_LOCAL)
+        R.refcuda_zfp_compress.restype = C.c_size_t
+        R.refcuda_zfp_compress.argtypes = [C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_uint, C.c_void_p,
+                                           C.c_size_t]
+        R.refcuda_zfp_decompress.restype = None
+        R.refcuda_zfp_decompress.argtypes = [C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_uint,
+                                             C.c_void_p]
+        R.refcuda_sparse_compress.restype = C.c_int
+        R.refcuda_sparse_compress.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                              C.c_void_p, C.c_void_p]
+        R.refcuda_sparse_decompress.restype = None
+        R.refcuda_sparse_decompress.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p,
+                                                C.c_void_p]
+        R.refcuda_sizeof_zfp_stream.restype = C.c_size_t
+        R.refcuda_sizeof_zfp_field.restype = C.c_size_t
+        _ref_cuda = R
+    return _ref_cuda
 
 
 def max_threads() -> int:

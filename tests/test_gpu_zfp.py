@@ -75,6 +75,23 @@ def test_generic_geometry(cs, oracle, dims, maxbits):
     _roundtrip(cs, oracle, a, dims, maxbits)
 
 
+@pytest.mark.parametrize("dims", [(4, 0, 0), (13, 0, 0), (5, 5, 5), (4, 4, 0), (12, 4, 4)])
+@pytest.mark.parametrize("maxbits", [32, 96, 160])
+def test_generic_odd_word_count_writes_every_byte(cs, oracle, dims, maxbits):
+    """Whole 32-bit words per block but an odd number of words in all: the last
+    32 bits of the 64-bit-sized stream belong to no block and must still be
+    written (as zeros), whatever the buffer held before."""
+    import torch
+    nx, ny, nz = dims
+    n = nx * max(ny, 1) * max(nz, 1)
+    a = util.normal(n, seed=n + maxbits)
+    need = cs.zfp_max_bytes(nx, ny, nz, maxbits)
+    out = torch.full((need,), 0xFF, dtype=torch.uint8, device="cuda")
+    cs.zfp_compress(torch.from_numpy(a).cuda(), maxbits, dims, out=out)
+    ref = oracle.zfp_encode(a, nx, ny, nz, maxbits)
+    assert np.array_equal(out.cpu().numpy().view(np.uint64), ref)
+
+
 def test_special_values(cs, oracle):
     n = 1024 * 16
     a = np.zeros(n, dtype=np.float32)
