@@ -14,10 +14,18 @@ each GPU.  Prints ONE JSON line:
             (host->device and device->host copies inside the timed region)
   cpu_baseline  the CPU codec (oracle port, OpenMP over blocks) on a bounded
             sample of the same data, on this host's cores
-  extra     sparse codec GB/s at 50/75/90 % zeros, swap-manager link numbers
+  extra     reference_cuda (the reference's own CUDA kernels on the same tensors,
+            when their build is present), link (plain pinned-copy ceiling with
+            all ranks copying at once), zfp_sweep (64 KiB .. 512 MiB x rates x
+            distributions), sparse codec at 50/75/90 % zeros, swap-manager
+            trips, vgg16 (swapped training step and the activation bytes that
+            can be swapped within a stated stretch of the step)
 
-`--impl reference` times the CPU implementation alone (the reference ships no
-CPU codec, so this is the oracle port pinned against the reference's headers).
+`--impl reference` times the CPU implementation on the whole tensor (the
+reference ships no CPU codec, so this is the oracle port, pinned against the
+reference's headers and against the output of its CUDA kernels) and, where a
+GPU and the reference's CUDA build are present, reports the reference's own
+kernels beside it.
 
 Multi-GPU: one process per GPU (torchrun), every rank codes its own tensor,
 no collective on the data path; time is the max over ranks.
@@ -52,6 +60,7 @@ def parse():
     ap.add_argument("--batch", type=int, default=0, help="batch size of the model workloads (0: 128 / 32)")
     ap.add_argument("--no-extra", action="store_true", help="skip the sparse / swap-link side measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-vgg", action="store_true", help="skip the swapped VGG16 step in the side measurements")
     return ap.parse_args()
 
 
@@ -119,12 +128,22 @@ class ClockSampler:
 # ---------------------------------------------------------------------------
 # CPU leg (oracle port); only place outside tests that runs oracle/
 # ---------------------------------------------------------------------------
+def host_threads() -> int:
+    """CPU threads this process may run on.  Counted from the affinity mask:
+    launchers such as torchrun export OMP_NUM_THREADS=1, which must not decide
+    how many cores the CPU codec gets."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_codec_sample(mib_total: int, rate: int, budget_s: float = 12.0):
     """Round-trip GB/s of the CPU codec on a bounded sample of the workload."""
     import numpy as np
     from oracle import oracle as O
     O.build()
-    threads = O.max_threads()
+    threads = host_threads()
     sample_mib = min(mib_total, max(8, 4 * threads))
     n = sample_mib * 262144
     rng = np.random.default_rng(0)
@@ -144,18 +163,90 @@ def cpu_codec_sample(mib_total: int, rate: int, budget_s: float = 12.0):
     return gbs, threads, f"{sample_mib} MiB slice of the {mib_total} MiB tensor, best of {reps} round trips"
 
 
+def reference_cuda_times(mib: int, rate: int, device=None):
+    """The reference's own CUDA kernels (cuZFP.cu / compression.cu compiled for
+    sm_100a, oracle/_ref/libcswap_ref_cuda.so) on this GPU: ZFP encode / decode
+    of the benchmark tensor and the sparse codec on config 2's tensor, timed
+    with CUDA events on the legacy default stream they run on.  None where the
+    build or a GPU is missing.  The calls include what the reference's entry
+    points do around the kernel (a cudaMemset of the stream and two device
+    synchronisations, cuZFP.cu:392-399, encode3.cuh:152)."""
+    try:
+        import torch
+        from oracle import oracle as O
+        if not (torch.cuda.is_available() and O.have_ref_cuda()):
+            return None
+        R = O.ref_cuda()
+    except Exception:
+        return None
+    dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+
+    def best_ms(fn, reps=3):
+        fn()
+        out = []
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            out.append(a.elapsed_time(b))
+        return min(out)
+
+    n = mib * 262144
+    nz, maxbits = n // 1024, 64 * rate
+    with torch.cuda.device(dev):
+        x = torch.tanh(torch.randn(n, device=dev, generator=torch.Generator(device=dev).manual_seed(1234)))
+        nbytes = n * rate // 8
+        buf = torch.zeros(nbytes + 4096, dtype=torch.uint8, device=dev)
+        y = torch.empty_like(x)
+        te = best_ms(lambda: R.refcuda_zfp_compress(x.data_ptr(), 32, 32, nz, maxbits, buf.data_ptr(), buf.numel()))
+        td = best_ms(lambda: R.refcuda_zfp_decompress(buf.data_ptr(), buf.numel(), 32, 32, nz, maxbits, y.data_ptr()))
+        res = {"zfp": {"tensor_mib": mib, "rate": rate, "encode_ms": te, "decode_ms": td,
+                       "roundtrip_uncompressed_GBps": 2 * 4 * n / ((te + td) * 1e-3) / 1e9},
+               "sparse": []}
+        del x, y, buf
+        ns = 128 * 128 * 16 * 16
+        P = 512 * 32
+        chunk = -(-ns // P)
+        begin = torch.zeros(P, dtype=torch.int32, device=dev)
+        num = torch.zeros(1, dtype=torch.int32, device=dev)
+        bitmap = torch.zeros(P * (-(-chunk // 32)), dtype=torch.int32, device=dev)
+        values = torch.zeros(ns, device=dev)
+        out = torch.zeros(ns, device=dev)
+        for zf, mu in ((0.5, 0.0), (0.75, -0.6745), (0.9, -1.2816)):
+            t = torch.relu(torch.randn(ns, device=dev, generator=torch.Generator(device=dev).manual_seed(7)) + mu)
+            tc = best_ms(lambda: R.refcuda_sparse_compress(t.data_ptr(), ns, 512, 32, begin.data_ptr(), num.data_ptr(),
+                                                           bitmap.data_ptr(), values.data_ptr()))
+            tdd = best_ms(lambda: R.refcuda_sparse_decompress(values.data_ptr(), out.data_ptr(), ns, 512, 32,
+                                                              bitmap.data_ptr(), begin.data_ptr()))
+            # the reference's scatter leaves the positions after a word's last set bit unwritten
+            # (compression.cu:281-292): check it on a zeroed destination, as its caller provides
+            out.zero_()
+            torch.cuda.synchronize()
+            R.refcuda_sparse_decompress(values.data_ptr(), out.data_ptr(), ns, 512, 32, bitmap.data_ptr(),
+                                        begin.data_ptr())
+            torch.cuda.synchronize()
+            res["sparse"].append({"tensor_mib": 16, "zero_fraction": zf, "compress_ms": tc, "decompress_ms": tdd,
+                                  "exact": bool(torch.equal(out, t))})
+    res["what"] = ("the reference's cuda_compress / cuda_decompress and PreGPUcompression+PreAcc+GPUcompression / "
+                   "GPUdecompression, device pointers, compiled for sm_100a from its own sources")
+    return res
+
+
 def run_reference(args):
-    """The reference arm: the CPU implementation of the path on this host."""
+    """The reference arm: the CPU implementation of the path on this host's
+    cores, whole tensor per step, every step and warm-up asked for; plus, where
+    possible, the reference's own CUDA kernels on this GPU."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    import numpy as np  # noqa: F401
+    import numpy as np
     from oracle import oracle as O
     O.build()
-    threads = O.max_threads()
-    import numpy as np
-    sample_mib = min(args.mib, max(8, 2 * threads))
-    n = sample_mib * 262144
+    threads = host_threads()
+    n = args.mib * 262144
     a = np.tanh(np.random.default_rng(0).standard_normal(n, dtype=np.float32))
     nz = n // 1024
 
@@ -163,24 +254,26 @@ def run_reference(args):
         s = O.zfp_encode(a, 32, 32, nz, 64 * args.rate, threads=threads)
         O.zfp_decode(s, 32, 32, nz, 64 * args.rate, threads=threads)
 
-    for _ in range(min(args.warmup, 2)):
+    for _ in range(args.warmup):
         step()
-    steps = max(1, min(args.steps, 10))
+    steps = max(1, args.steps)
     t0 = time.perf_counter()
     for _ in range(steps):
         step()
     dt = (time.perf_counter() - t0) / steps
     gbs = 2 * 4 * n / dt / 1e9
-    sample = f"{sample_mib} MiB slice per step, {steps} timed steps (of {args.steps} requested), {threads} OpenMP threads"
+    sample = f"the whole {args.mib} MiB tensor per step, {steps} timed steps, {threads} OpenMP threads"
     line = {
         "impl": "reference", "metric": "zfp_roundtrip_uncompressed_GBps", "value": gbs, "unit": "GB/s",
-        "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 2), "ms_per_step": dt * 1e3,
+        "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32->i32/u64", "data": "synthetic",
         "config": workload_config(args),
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "note": "the reference has no CPU codec (zfp.c is stripped); this is the CPU restatement of its GPU "
-                "algorithm, pinned against a host build of the reference's own headers",
+        "reference_cuda": reference_cuda_times(args.mib, args.rate),
+        "note": "the reference has no CPU codec (zfp.c is stripped); `value` is the CPU restatement of its GPU "
+                "algorithm, pinned against a host build of the reference's own headers and against the output "
+                "of its CUDA kernels; reference_cuda times those kernels themselves on this GPU",
     }
     print(json.dumps(line))
 
@@ -357,6 +450,135 @@ def run_model_workload(args):
         dist.destroy_process_group()
 
 
+def hidden_bytes_sweep(W, cs, torch, model, mgr, make_batch, prof, policy_of, t_no_swap_ms, eps_list,
+                       steps=6, warmup=2):
+    """How many activation bytes can be swapped out and back within a stated
+    stretch of the step.  Candidates are the activations autograd keeps for
+    backward, largest first; the k largest are swapped under `policy_of(id)`,
+    for k = 0, 1, 2, ...; a point is "hidden" at eps when its median step time
+    stays within (1 + eps) of the no-swap step.  Returns, per eps, the largest
+    swapped activation bytes among the hidden points, and the measured curve."""
+    ids = [i for i, p in prof.items() if p["saved"] and p["float32"] and p["has_grad"] and not p["omit"]
+           and p["numel"] >= 1 << 18]
+    consumer = {}
+    for idx in sorted(prof):
+        for tid in prof[idx]["inputs"]:
+            consumer.setdefault(tid, idx)
+    ids = [i for i in ids if i in consumer]
+    ids.sort(key=lambda i: -prof[i]["numel"])
+    nids = max(prof) + 2
+    curve = []
+    ks = list(range(0, len(ids) + 1))
+    for k in ks:
+        exe = cs.Execution(mgr=mgr)
+        exe.init_(nids)
+        for tid in ids[:k]:
+            exe.policy[tid] = policy_of(tid)
+            exe.begin_stage[tid] = consumer[tid]
+        r = W.timed_steps(model, exe, make_batch, steps, warmup)
+        # bytes that went out AND came back through the link (a lossless tensor taken back
+        # before it had left the device is not counted)
+        curve.append({"k": k, "ms_median": r["ms_median"], "activation_bytes": r["activation_bytes_back_per_step"],
+                      "link_bytes_out": r["link_bytes_out_per_step"], "link_bytes_in": r["link_bytes_in_per_step"]})
+    hidden = {}
+    for eps in eps_list:
+        ok = [c["activation_bytes"] for c in curve if c["ms_median"] <= (1 + eps) * t_no_swap_ms]
+        hidden[f"{eps:g}"] = max(ok) if ok else 0.0
+    return {"candidates": len(ids), "hidden_activation_bytes": hidden, "curve": curve}
+
+
+def vgg16_block(args, cs, torch, dev, world, rank):
+    """The swapped VGG16 training step (batch 128, 3x32x32 synthetic inputs,
+    CSWAP+/vgg16-cifar10.cpp:135-245) on every rank at once: step time, link
+    bytes and peak device memory without swapping, with raw swap of every
+    kept activation, with the reference's hard-wired split, self-tuned, and
+    with ZFP-8 on everything; then the activation bytes each of raw swap and
+    compressed swap can move within a stated stretch of the no-swap step."""
+    from cswap_b200 import workloads as W
+    torch.manual_seed(1 + rank)
+    batch = 128
+    model = W.VGG16().to(dev).train()
+    hx = torch.randn(batch, 3, 32, 32).pin_memory()
+    hy = torch.randint(0, 10, (batch,)).pin_memory()
+    mgr = cs.SwapManager(pinned_bytes=2 << 30, staging_bytes=512 << 20, zfp_maxbits=512)
+    make_batch = lambda: (hx, hy)
+    nids, steps, warmup = 64, 10, 3
+
+    def fresh(policy_fn):
+        exe = cs.Execution(mgr=mgr)
+        exe.init_(nids)
+        policy_fn(exe)
+        return exe
+
+    def every(pol):
+        def f(exe):
+            for i in range(nids):
+                exe.begin_stage[i] = i + 1
+                exe.policy[i] = pol
+        return f
+
+    rows = {}
+    rows["no_swap"] = W.timed_steps(model, fresh(lambda e: None), make_batch, steps, warmup)
+    rows["raw_swap"] = W.timed_steps(model, fresh(every(cs.POLICY_RAW)), make_batch, steps, warmup)
+    rows["reference_split_zfp8"] = W.timed_steps(model, fresh(W.vgg16_reference_policy), make_batch, steps, warmup)
+    rows["zfp8_everywhere"] = W.timed_steps(model, fresh(every(cs.POLICY_ZFP)), make_batch, steps, warmup)
+    # self-tuned: profile one step, fit the cost model on this GPU with the other ranks busy too, decide
+    exe = fresh(lambda e: None)
+    exe.profile = True
+    x, y = hx.to(dev).requires_grad_(True), hy.to(dev)
+    model.forward_with(exe, x, y).backward()
+    prof = exe.finish_profile()
+    cm = cs.CostModel.fit(mgr, 512)
+    cands = exe.policy_candidates(prof, cm)
+    chosen = exe.refine_policy(cands, lambda k: W.timed_steps(model, exe, make_batch, k, 0)["ms_per_step"] * k * 1e-3)
+    tuned_policy = list(exe.policy)
+    rows["self_tuned"] = W.timed_steps(model, exe, make_batch, steps, warmup)
+    t0 = rows["no_swap"]["ms_median"]
+    eps_list = (0.1, 0.25, 0.5, 1.0)
+    lossless = {tid: (cs.POLICY_SPARSE if p["zero_fraction"] >= 0.3 else cs.POLICY_RAW) for tid, p in prof.items()}
+    sweeps = {
+        "raw": hidden_bytes_sweep(W, cs, torch, model, mgr, make_batch, prof, lambda tid: cs.POLICY_RAW, t0, eps_list),
+        # the reference's rule for where loss is allowed: ZFP-8 on conv inputs, lossless elsewhere
+        "compressed_reference_rule": hidden_bytes_sweep(
+            W, cs, torch, model, mgr, make_batch, prof,
+            lambda tid: cs.POLICY_ZFP if tid in W.VGG_CONV_INPUT_IDS else lossless.get(tid, cs.POLICY_RAW), t0,
+            eps_list),
+        "compressed_zfp8_everywhere": hidden_bytes_sweep(W, cs, torch, model, mgr, make_batch, prof,
+                                                         lambda tid: cs.POLICY_ZFP, t0, eps_list),
+    }
+    ratios = {}
+    for name in ("compressed_reference_rule", "compressed_zfp8_everywhere"):
+        ratios[name] = {e: (sweeps[name]["hidden_activation_bytes"][e] / sweeps["raw"]["hidden_activation_bytes"][e]
+                            if sweeps["raw"]["hidden_activation_bytes"][e] > 0 else None)
+                        for e in sweeps["raw"]["hidden_activation_bytes"]}
+    # the slowest rank's step time per row
+    names = list(rows)
+    worst = max_over_ranks([rows[k]["ms_median"] for k in names], dev)
+    out = {"batch": batch, "ranks_running": world, "host_side": "python saved-tensor hooks (cswap_b200/execution.py)",
+           "steps": steps, "warmup": warmup,
+           "rows": {k: {"ms_per_step_median": rows[k]["ms_median"], "ms_per_step_median_slowest_rank": w,
+                        "activation_bytes_swapped": rows[k]["activation_bytes_per_step"],
+                        "link_bytes_out": rows[k]["link_bytes_out_per_step"],
+                        "link_bytes_in": rows[k]["link_bytes_in_per_step"],
+                        "peak_device_mib": round(rows[k]["peak_device_bytes"] / 2**20, 1)}
+                    for k, w in zip(names, worst)},
+           "self_tuned_policy_counts": {str(c): tuned_policy.count(c) for c in (0, 2, 3, 6)},
+           "self_tuned_chosen": chosen,
+           "hidden_activation_bytes": {
+               "definition": "uncompressed activation bytes swapped out and back per step by the configuration "
+                             "that swaps the most while the median step stays within (1 + eps) of the no-swap "
+                             "step; candidates are the kept activations, largest first",
+               "eps": list(eps_list), "no_swap_ms": t0,
+               "per_policy": {k: v["hidden_activation_bytes"] for k, v in sweeps.items()},
+               "ratio_to_raw": ratios, "target_ratio": 2.0,
+               "curves": {k: v["curve"] for k, v in sweeps.items()}},
+           "cost_model": cm.as_dict()}
+    mgr.close()
+    del model
+    torch.cuda.empty_cache()
+    return out
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -434,6 +656,26 @@ def main():
     ms_per_step = t_total / args.steps * 1e3
     value = whole_job_gbps(world, 2 * 4 * n, t_total / args.steps)
 
+    # A second, longer region of the same step (at least half a second of device time), so that
+    # the clock samples show what the step does to the clocks; the headline stays the K steps asked for.
+    per_step = max(t_total / args.steps, 1e-6)
+    long_steps = max(args.steps, int(0.6 / per_step) + 1)
+    sampler.start()
+    l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    l0.record()
+    for _ in range(long_steps):
+        cs.zfp_compress(x, maxbits, out=comp)
+        cs.zfp_decompress(comp, n, maxbits, out=y)
+        if flush is not None:
+            flush.fill_(1)
+    l1.record()
+    torch.cuda.synchronize()
+    sampler.stop()
+    t_long = max_over_ranks([l0.elapsed_time(l1) * 1e-3], dev)[0]
+
     # ---- end to end through the reference-named entry points, host buffers ----
     import ctypes as C
     from cswap_b200._lib import Bitstream, ZfpField, ZfpStream
@@ -475,8 +717,8 @@ def main():
     peak, peak_kind = load_peaks()
     alg = 4 * n + n * args.rate // 8
     name, t_k = ("zfp_encode_slab_kernel", t_enc) if t_enc >= t_dec else ("zfp_decode_slab_kernel", t_dec)
-    # DRAM read + write bytes of one launch from the committed ncu capture of this exact
-    # workload (profiles/zfp_slab_kernels_256MiB_rate8.md); unknown for other sizes / rates
+    # DRAM read + write bytes of one launch, from an ncu capture of this exact workload
+    # (256 MiB tensor, rate 8); unknown for other sizes / rates
     ncu_traffic = {("zfp_encode_slab_kernel", 256, 8): 317.7e6, ("zfp_decode_slab_kernel", 256, 8): 276.2e6}
     roofline = {"bound": "hbm", "kernel": name, "achieved": alg / t_k / 1e9, "peak": peak, "unit": "GB/s",
                 "frac": alg / t_k / 1e9 / peak, "peak_kind": f"of {peak_kind}", "traffic": ncu_traffic.get((name, args.mib, args.rate)),
@@ -487,7 +729,17 @@ def main():
 
     extra = {}
     if not args.no_extra:
-        extra = side_measurements(cs, torch, dev, peak)
+        extra = side_measurements(cs, torch, dev, peak, world, args)
+        # The two calls block, as the reference's do, so they cannot overlap each other: each is
+        # bound by its larger direction (the field in, then the field out).  Against the measured
+        # one-direction copy rates with every rank copying at once.
+        lk = extra["link"]
+        t_floor = max(4 * n / lk["h2d_GBps_per_gpu"], stream_bytes / lk["d2h_GBps_per_gpu"]) / 1e9 + \
+            max(stream_bytes / lk["h2d_GBps_per_gpu"], 4 * n / lk["d2h_GBps_per_gpu"]) / 1e9
+        e2e["link_floor_ms_per_step"] = t_floor * 1e3
+        e2e["fraction_of_link_ceiling"] = t_floor / t_e2e
+        if not args.no_vgg:
+            extra["vgg16"] = vgg16_block(args, cs, torch, dev, world, rank)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -495,23 +747,158 @@ def main():
         cpu = {"value": v, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
 
     clocks = sampler.summary()
+    sustained = {"steps": long_steps, "seconds": t_long, "ms_per_step": t_long / long_steps * 1e3,
+                 "value": whole_job_gbps(world, 2 * 4 * n, t_long / long_steps), "unit": "GB/s",
+                 "ms_per_step_x_median_sm_mhz": (t_long / long_steps * 1e3 * clocks["sm_mhz"]) if clocks["sm_mhz"]
+                 else None}
     if rank == 0:
         line = {
             "metric": "zfp_roundtrip_uncompressed_GBps", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32->i32/u64", "data": "synthetic",
             "config": workload_config(args), "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
-            "gpu_launches": 2 * args.steps, "clocks": clocks, "extra": extra,
+            "gpu_launches": 2 * args.steps, "clocks": clocks, "sustained": sustained, "extra": extra,
         }
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 
 
-def side_measurements(cs, torch, dev, peak):
-    """Sparse codec throughput per sparsity (16 MiB and 256 MiB tensors) and the
-    swap manager's host-link numbers.  Reported beside the headline, not in it."""
-    out = {"sparse": [], "swap": {}, "zfp_rates": []}
+def link_ceiling(torch, dev, world):
+    """What the host link gives a plain copy: pinned device-to-host only,
+    host-to-device only and both directions at once, 256 MiB per copy by
+    cudaMemcpyAsync, with every rank of the job starting behind one barrier -
+    the ceiling for anything that swaps (the raw-swap copy of
+    CSWAP+/Execution.h:70-85 run by all replicas at once).  GB/s per GPU is the
+    slowest rank's; the job's aggregate is that times the rank count."""
+    import torch.distributed as dist
+    nbytes = 256 << 20
+    d_a = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+    d_b = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    h_a = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    h_b = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    h_b.copy_(d_a)  # both host buffers have been written before they are read
+    s1, s2 = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+
+    def run(kind, reps=6):
+        best = float("inf")
+        for r in range(reps + 1):
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            e0.record()
+            s1.wait_event(e0)
+            s2.wait_event(e0)
+            if kind in ("d2h", "both"):
+                with torch.cuda.stream(s1):
+                    h_a.copy_(d_a, non_blocking=True)
+            if kind in ("h2d", "both"):
+                with torch.cuda.stream(s2):
+                    d_b.copy_(h_b, non_blocking=True)
+            e1.record(s1)
+            e2.record(s2)
+            torch.cuda.synchronize()
+            dt = max(e0.elapsed_time(e1), e0.elapsed_time(e2)) * 1e-3
+            if r:
+                best = min(best, dt)
+        return max_over_ranks([best], dev)[0]
+
+    t_out, t_in, t_both = run("d2h"), run("h2d"), run("both")
+    return {"bytes_per_copy": nbytes, "ranks_copying": world,
+            "d2h_GBps_per_gpu": nbytes / t_out / 1e9, "h2d_GBps_per_gpu": nbytes / t_in / 1e9,
+            "both_GBps_per_gpu_each_way": nbytes / t_both / 1e9,
+            "both_GBps_aggregate_both_ways": 2 * world * nbytes / t_both / 1e9}
+
+
+def zfp_sweep(cs, torch, dev, peak, flush):
+    """Encode and decode time of every point of the size sweep: 64 KiB .. 512 MiB
+    (nx = ny = 32, nz scaled) x rates 4 / 8 / 16 x values N(0,1) and U[-1,1].
+    L2 is flushed before every timed call; `frac` is algorithmic bytes
+    (4N + N*rate/8) over time against the measured HBM peak."""
+    rows = []
+
+    def med(fn, reps):
+        fn()
+        ts = []
+        for _ in range(reps):
+            flush.fill_(0)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1e-3)
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    for dist_name in ("normal", "uniform"):
+        g = torch.Generator(device=dev).manual_seed(99)
+        big = torch.randn(512 * 262144, device=dev, generator=g) if dist_name == "normal" else \
+            torch.rand(512 * 262144, device=dev, generator=g) * 2 - 1
+        back = torch.empty_like(big)
+        comp = torch.empty(cs.zfp_max_bytes(32, 32, big.numel() // 1024, 1024), dtype=torch.uint8, device=dev)
+        kib = 64
+        while kib <= 512 * 1024:
+            n = kib * 256
+            t = big[:n]
+            reps = 7 if kib <= 65536 else 3
+            for rate in (4, 8, 16):
+                mb = 64 * rate
+                te = med(lambda: cs.zfp_compress(t, mb, out=comp), reps)
+                td = med(lambda: cs.zfp_decompress(comp, n, mb, out=back[:n]), reps)
+                alg = 4 * n + n * rate // 8
+                rows.append({"kib": kib, "rate": rate, "dist": dist_name, "encode_us": te * 1e6, "decode_us": td * 1e6,
+                             "encode_GBps_uncompressed": 4 * n / te / 1e9, "decode_GBps_uncompressed": 4 * n / td / 1e9,
+                             "encode_frac_hbm": alg / te / 1e9 / peak, "decode_frac_hbm": alg / td / 1e9 / peak})
+            kib *= 2
+        del big, back, comp
+    return rows
+
+
+def swap_trips(cs, torch, dev):
+    """One tensor out to pinned host memory and back through the swap manager,
+    per policy: raw, ZFP rate 8 and sparse at 50 / 75 / 90 % zeros (64 MiB
+    tensor).  The trip waits for the copy out and gives the staging copy up
+    before it asks for the tensor back, so every policy crosses the link in
+    both directions; link bytes each way are the manager's own counters."""
+    out = {}
+    mgr = cs.SwapManager(pinned_bytes=512 << 20, staging_bytes=256 << 20)
+    n = 64 * 262144
+    g = torch.Generator(device=dev).manual_seed(5)
+    dense = torch.tanh(torch.randn(n, device=dev, generator=g))
+    dst = torch.empty_like(dense)
+    cases = [("raw", cs.POLICY_RAW, dense), ("zfp8", cs.POLICY_ZFP, dense)]
+    for zf, mu in ((50, 0.0), (75, -0.6745), (90, -1.2816)):
+        cases.append((f"sparse_{zf}", cs.POLICY_SPARSE, torch.relu(torch.randn(n, device=dev, generator=g) + mu)))
+        cases.append((f"raw_of_sparse_{zf}", cs.POLICY_RAW, cases[-1][2]))
+    for name, pol, t in cases:
+        def trip():
+            tk = mgr.swap_out(t, pol)
+            mgr.sync()             # the copy out has landed and the staging copy is given up
+            mgr.swap_in(tk, out=dst)
+            torch.cuda.synchronize()
+            tk.release()
+        trip()
+        mgr.reset_stats()
+        reps = 5
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            trip()
+        dt = (time.perf_counter() - t0) / reps
+        st = mgr.stats()
+        exact = bool(torch.equal(dst.view(torch.int32), t.view(torch.int32)))
+        out[name] = {"tensor_mib": 64, "out_plus_in_ms": dt * 1e3, "uncompressed_GBps": 2 * 4 * n / dt / 1e9,
+                     "link_bytes_out": st["moved_bytes_out"] // reps, "link_bytes_in": st["moved_bytes_in"] // reps,
+                     "link_GBps": (st["moved_bytes_out"] + st["moved_bytes_in"]) / reps / dt / 1e9,
+                     "bit_exact": exact}
+    mgr.close()
+    return out
+
+
+def side_measurements(cs, torch, dev, peak, world=1, args=None):
+    """Measurements reported beside the headline, not in it."""
+    out = {"link": link_ceiling(torch, dev, world), "sparse": [], "swap": {}, "zfp_rates": []}
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
     def timeit(fn, reps=10):
@@ -549,38 +936,14 @@ def side_measurements(cs, torch, dev, peak):
                 "decompress_frac_hbm": alg / td / 1e9 / peak,
                 "exact": bool(torch.equal(back.view(torch.int32), t.view(torch.int32)))})
             del t, packed, back
-    # the ZFP kernels at the other two rates the reference's drivers use (256 MiB tensor)
-    n = 256 * 262144
-    t = torch.tanh(torch.randn(n, device=dev))
-    back = torch.empty_like(t)
-    for rate in (4, 8, 16):
-        mb = 64 * rate
-        comp = torch.empty(cs.zfp_max_bytes(32, 32, n // 1024, mb), dtype=torch.uint8, device=dev)
-        te = timeit(lambda: cs.zfp_compress(t, mb, out=comp))
-        td = timeit(lambda: cs.zfp_decompress(comp, n, mb, out=back))
-        alg = 4 * n + n * rate // 8
-        out["zfp_rates"].append({"tensor_mib": 256, "rate": rate, "encode_ms": te * 1e3, "decode_ms": td * 1e3,
-                                 "encode_frac_hbm": alg / te / 1e9 / peak, "decode_frac_hbm": alg / td / 1e9 / peak})
-        del comp
-    del t, back
-    # swap link: raw vs ZFP-8 swap-out + swap-in of a 64 MiB tensor through the manager
-    mgr = cs.SwapManager(pinned_bytes=512 << 20, staging_bytes=256 << 20)
-    n = 64 * 262144
-    t = torch.tanh(torch.randn(n, device=dev))
-    dst = torch.empty_like(t)
-    for name, pol in (("raw", cs.POLICY_RAW), ("zfp8", cs.POLICY_ZFP)):
-        def trip():
-            tk = mgr.swap_out(t, pol)
-            mgr.swap_in(tk, out=dst)
-            torch.cuda.synchronize()
-            tk.release()
-        trip()
-        t0 = time.perf_counter()
-        for _ in range(5):
-            trip()
-        dt = (time.perf_counter() - t0) / 5
-        out["swap"][name] = {"tensor_mib": 64, "out_plus_in_ms": dt * 1e3, "uncompressed_GBps": 2 * 4 * n / dt / 1e9}
-    mgr.close()
+    out["zfp_sweep"] = zfp_sweep(cs, torch, dev, peak, flush)
+    out["zfp_rates"] = [r for r in out["zfp_sweep"] if r["kib"] == 256 * 1024 and r["dist"] == "normal"]
+    del flush
+    out["swap"] = swap_trips(cs, torch, dev)
+    try:
+        out["reference_cuda"] = reference_cuda_times(args.mib if args else 256, args.rate if args else 8, dev)
+    except Exception as err:  # the checker's build is optional
+        out["reference_cuda"] = {"unavailable": repr(err)}
     return out
 
 

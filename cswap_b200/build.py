@@ -53,27 +53,40 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
-def build_cpp_driver(force: bool = False) -> str:
-    """Compile tests/cpp/execution_driver.cpp (the C++ Execution class over stock
-    libtorch) against the in-tree library with g++."""
+CPP_DRIVERS = ("execution_driver", "vgg16_step")
+
+
+def build_cpp_driver(force: bool = False, name: str = "execution_driver") -> str:
+    """Compile tests/cpp/<name>.cpp (drivers written against the C++ Execution
+    class over stock libtorch, include/cswap_execution.hpp) against the in-tree
+    library with g++."""
     import torch
     root = os.path.dirname(HERE)
-    src = os.path.join(root, "tests", "cpp", "execution_driver.cpp")
-    hdr = os.path.join(root, "include", "cswap_execution.hpp")
-    exe = os.path.join(root, "tests", "cpp", "execution_driver")
-    if not force and os.path.exists(exe) and all(os.path.getmtime(exe) >= os.path.getmtime(f) for f in (src, hdr)):
+    src = os.path.join(root, "tests", "cpp", name + ".cpp")
+    hdrs = [os.path.join(root, "include", h) for h in ("cswap_execution.hpp", "cswap_b200.h")]
+    exe = os.path.join(root, "tests", "cpp", name)
+    if not force and os.path.exists(exe) and all(os.path.getmtime(exe) >= os.path.getmtime(f) for f in [src] + hdrs):
         return exe
     build()
     t = os.path.dirname(torch.__file__)
     cuda_inc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
+    # the CUDA runtime libtorch itself is linked against (its wheel ships one), else the toolkit's
+    import glob
+    rt = sorted(glob.glob(os.path.join(os.path.dirname(t), "nvidia", "cuda_runtime", "lib", "libcudart.so.*")))
+    rt = rt[0] if rt else os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "lib64", "libcudart.so")
     cmd = ["g++", "-std=c++17", "-O1", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
            "-I", os.path.join(root, "include"), "-I", os.path.join(t, "include"),
            "-I", os.path.join(t, "include", "torch", "csrc", "api", "include"), "-I", cuda_inc, src, "-o", exe,
            "-L", os.path.join(t, "lib"), "-L", HERE, f"-Wl,-rpath,{os.path.join(t, 'lib')}",
            "-Wl,-rpath,$ORIGIN/../../cswap_b200", "-Wl,--no-as-needed",
-           "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda", "-lcswap_b200"]
+           "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda", "-lcswap_b200", rt,
+           f"-Wl,-rpath,{os.path.dirname(rt)}", "-Wno-interference-size"]
     subprocess.check_call(cmd)
     return exe
+
+
+def build_cpp_drivers(force: bool = False):
+    return [build_cpp_driver(force, n) for n in CPP_DRIVERS]
 
 
 if __name__ == "__main__":

@@ -212,6 +212,7 @@ def timed_steps(model: nn.Module, exe: Execution, make_batch: Callable[[], Tuple
     times.sort()
     return {"ms_per_step": sum(times) / n, "ms_median": times[len(times) // 2], "loss": loss_val,
             "swapped_tensors_per_step": s["swap_outs"] / n, "activation_bytes_per_step": s["raw_bytes_out"] / n,
+            "activation_bytes_back_per_step": s["raw_bytes_in"] / n,
             "link_bytes_out_per_step": s["moved_bytes_out"] / n, "link_bytes_in_per_step": s["moved_bytes_in"] / n,
             "pinned_high_water": s["pinned_high_water"], "staging_high_water": s["staging_high_water"],
             "peak_device_bytes": torch.cuda.max_memory_allocated(),

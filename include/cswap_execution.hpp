@@ -2,37 +2,49 @@
 // stock libtorch, over the C ABI of libcswap_b200.so.
 //
 // Same surface as the reference class: init_, preforward, pre, post,
-// postforward, the public tables policy / begin_stage / types, index and
-// policy_, the Layer_type enum (Execution.h:28-35) and the policy codes
-// 0 keep, 2 raw, 3 sparse, 6 ZFP.  A driver wraps each layer exactly as the
-// reference's drivers do (vgg16-cifar10.cpp:219-226):
+// postforward, setRatio, the public tables policy / begin_stage / types, index
+// and policy_, the Layer_type enum (Execution.h:28-35) and the policy codes
+// 0 keep, 1 drop and rebuild, 2 raw, 3 sparse, 6 ZFP.  A driver wraps each
+// layer exactly as the reference's drivers do (vgg16-cifar10.cpp:219-226):
 //
-//     exe.pre(pre);  x = layer(pre);  exe.post(pre, x);  pre = x;
+//     exe.pre(pre, type);  x = layer(pre);  exe.post(pre, x, type, false, layer);  pre = x;
 //
 // What is different underneath:
 //  * the fork-only members the reference writes (Tensor::tensor_id,
-//    Node::com_and_tran / storage_impl_ / pre_node ...) do not exist upstream;
-//    tensor ids are kept in a side table keyed by the tensor's TensorImpl and
-//    the swap-in runs from a FunctionPreHook on the consumer's grad_fn, which
+//    Node::com_and_tran / storage_impl_ / pre_node / func_ ...) do not exist
+//    upstream; tensor ids are kept in a side table keyed by the tensor's
+//    TensorImpl, the producer the reference stores in grad_fn()->func_
+//    (vgg16-cifar10.cpp:223) is the optional last argument of post(), and the
+//    swap-in runs from a FunctionPreHook on the consumer's grad_fn, which
 //    autograd always runs before the producer's own backward;
 //  * swap-out and swap-in go through csw_swap_out / csw_swap_in: events between
 //    streams, pooled pinned memory, no stream synchronisation, no blocking read
 //    of the sparse count (Execution.h:77,92,236);
 //  * a tensor's device block is handed back to the caching allocator only once
-//    the manager's streams have finished reading it (polled, never waited for).
+//    the manager's streams have finished reading it (polled, never waited for);
+//  * a tensor that nothing holds for backward once its consumer has run is not
+//    copied out at all, and a losslessly swapped tensor that backward asks for
+//    before its copy out has finished is handed back as it is;
+//  * the profiling record the reference sends to its policy maker
+//    (Execution.h:220-234,318-331) is kept per layer here and make_policy()
+//    turns it into a policy table through csw_cost_fit / csw_cost_decide.
 //
 // Constraints inherited from the reference's scheme: begin_stage[id] must be the
 // LAST forward use of tensor id (its storage is empty afterwards until backward
 // restores it), and only whole, contiguous float32 CUDA storages are swapped.
-// Policy 1 (drop and recompute) is not implemented: such tensors are kept.
 #pragma once
+#include <ATen/cuda/CUDAEvent.h>
 #include <c10/cuda/CUDACachingAllocator.h>
 #include <c10/cuda/CUDAStream.h>
 #include <torch/csrc/autograd/function.h>
 #include <torch/csrc/autograd/function_hook.h>
 #include <torch/torch.h>
 
+#include <algorithm>
+#include <functional>
+#include <map>
 #include <memory>
+#include <set>
 #include <stdexcept>
 #include <string>
 #include <unordered_map>
@@ -43,6 +55,21 @@
 namespace cswap {
 
 enum Layer_type { CONV, POOL, ACT, BN, FC, MASKFILL };
+
+using Producer = std::function<torch::Tensor(const torch::Tensor&)>;
+
+// What one profiled layer recorded (Execution.h:220-234): its time, the size
+// and sparsity of its output, which tensors it consumed and whether anything
+// keeps its output for backward.
+struct LayerProfile {
+  double time_s = 0;
+  size_t numel = 0;
+  double zero_fraction = -1;
+  std::vector<int> inputs;
+  bool omit = false;
+  int type = ACT;
+  bool float32 = false, has_grad = false, saved = true, recomputable = false;
+};
 
 class Execution {
  public:
@@ -69,15 +96,23 @@ class Execution {
     } else {
       check(csw_mgr_set_zfp_maxbits(mgr_, zfp_maxbits), "csw_mgr_set_zfp_maxbits");
     }
+    maxbits_ = zfp_maxbits;
   }
-  void setRatio(unsigned maxbits) { check(csw_mgr_set_zfp_maxbits(mgr_, maxbits), "csw_mgr_set_zfp_maxbits"); }
+  void setRatio(unsigned maxbits) {
+    check(csw_mgr_set_zfp_maxbits(mgr_, maxbits), "csw_mgr_set_zfp_maxbits");
+    maxbits_ = maxbits;
+  }
 
   // Execution.h:403-412
   void preforward() {
     index = -1;
     ids_.clear();
     pending_.clear();
+    deferred_.clear();
     order_.clear();
+    by_storage_.clear();
+    producers_.clear();
+    seen_.clear();
     poll();
   }
   void postforward() { poll(); }
@@ -85,22 +120,127 @@ class Execution {
   // Execution.h:65-133
   void pre(torch::Tensor& t, Layer_type layer_type = ACT) {
     index++;
+    seen_.clear();
+    note_input(t);
     maybe_swap_out(t, layer_type);
+    begin_profile();
   }
   // Execution.h:135-212
   void pre(std::vector<torch::Tensor> inputs, Layer_type layer_type = ACT) {
     index++;
+    seen_.clear();
+    for (auto& t : inputs) note_input(t);
     for (auto& t : inputs) maybe_swap_out(t, layer_type);
+    begin_profile();
   }
-  // Execution.h:217-310
-  void post(torch::Tensor& pre_t, torch::Tensor& x, Layer_type = ACT, bool = false) {
-    (void)pre_t;
-    finish_layer(x);
+  // Execution.h:217-310.  `producer`, when given, is the layer itself: what
+  // rebuilds x from pre_t should x be dropped under policy 1.
+  void post(torch::Tensor& pre_t, torch::Tensor& x, Layer_type layer_type = ACT, bool isomit = false,
+            Producer producer = nullptr) {
+    torch::Tensor* in[1] = {&pre_t};
+    finish_layer(in, 1, x, layer_type, isomit, std::move(producer));
   }
   // Execution.h:311-401
-  void post(std::vector<torch::Tensor> inputs, torch::Tensor& x, Layer_type = ACT, bool = false) {
-    (void)inputs;
-    finish_layer(x);
+  void post(std::vector<torch::Tensor> inputs, torch::Tensor& x, Layer_type layer_type = ACT, bool isomit = false) {
+    std::vector<torch::Tensor*> in;
+    for (auto& t : inputs) in.push_back(&t);
+    finish_layer(in.data(), in.size(), x, layer_type, isomit, nullptr);
+  }
+
+  // ---- self-tuning (call sites Execution.h:224-233, resnet-cifar10.cpp:407-437) ----
+  // Set before a forward + backward pass to record it; finish_profile() turns
+  // the events into numbers (synchronises the device).
+  bool profile = false;
+  std::map<int, LayerProfile> finish_profile() {
+    c10::cuda::device_synchronize();
+    std::map<int, LayerProfile> out;
+    for (auto& kv : prof_) {
+      LayerProfile p = kv.second.p;
+      p.time_s = kv.second.start.elapsed_time(kv.second.end) * 1e-3;
+      if (kv.second.zeros.defined()) p.zero_fraction = kv.second.zeros.item<double>();
+      out[kv.first] = p;
+    }
+    prof_.clear();
+    profile = false;
+    return out;
+  }
+
+  // The fitted cost model of this device (measured once, on first use).
+  const csw_cost_model& cost_model() {
+    if (!fitted_) {
+      cost_ = csw_cost_model{};
+      cost_.zfp_maxbits = maxbits_;
+      check(csw_cost_fit(mgr_, &cost_), "csw_cost_fit");
+      fitted_ = true;
+    }
+    return cost_;
+  }
+
+  // Fill policy / begin_stage from a profiled iteration.  Tensor id i (the
+  // output of layer i) becomes a swap candidate at the first layer that
+  // consumes it; the cost model gets the forward time at which that consumer
+  // starts and the backward compute that precedes the consumer's backward
+  // (bwd_factor times the forward time of the later layers) and simulates the
+  // step's link traffic to choose raw / sparse / ZFP.  ZFP is allowed on
+  // `lossy_ids` (nullptr: the inputs of CONV layers, where the reference's
+  // drivers apply it, vgg16-cifar10.cpp:381-397).  `all_zfp_where_allowed`
+  // builds the table's neighbour instead: ZFP on every tensor where loss is
+  // allowed, the model's choice elsewhere.
+  std::vector<int> make_policy(const std::map<int, LayerProfile>& prof, const std::set<int>* lossy_ids = nullptr,
+                               double bwd_factor = 2.0, size_t min_bytes = size_t(1) << 20,
+                               bool all_zfp_where_allowed = false) {
+    const int n = prof.empty() ? 0 : prof.rbegin()->first + 1;
+    std::vector<double> start(n + 1, 0.0);
+    for (int i = 0; i < n; i++) {
+      auto it = prof.find(i);
+      start[i + 1] = start[i] + (it == prof.end() ? 0.0 : it->second.time_s);
+    }
+    const double fwd_total = start[n];
+    std::map<int, int> consumer;
+    std::set<int> conv_inputs;
+    for (auto& kv : prof)
+      for (int tid : kv.second.inputs)
+        if (tid >= 0 && !consumer.count(tid)) {
+          consumer[tid] = kv.first;
+          if (kv.second.type == CONV) conv_inputs.insert(tid);
+        }
+    const std::set<int>& lossy = lossy_ids ? *lossy_ids : conv_inputs;
+    if ((int)policy.size() < n) {
+      policy.resize(n, 0);
+      begin_stage.resize(n, 0);
+    }
+    std::vector<std::pair<int, int>> by_consumer;  // (consumer, id)
+    for (auto& kv : consumer) by_consumer.push_back({kv.second, kv.first});
+    std::sort(by_consumer.begin(), by_consumer.end());
+    std::vector<int> cands;
+    std::vector<csw_tensor_desc> descs;
+    for (auto& ci : by_consumer) {
+      auto it = prof.find(ci.second);
+      if (it == prof.end()) continue;
+      const LayerProfile& p = it->second;
+      if (p.omit || !p.float32 || !p.has_grad || p.numel * 4 < min_bytes || !p.saved) continue;
+      csw_tensor_desc d{};
+      d.numel = p.numel;
+      d.zero_fraction = p.zero_fraction;
+      d.lossy_ok = lossy.count(ci.second) ? 1 : 0;
+      d.ready_s = start[ci.first];
+      d.need_s = bwd_factor * (fwd_total - start[ci.first + 1]);
+      cands.push_back(ci.second);
+      descs.push_back(d);
+    }
+    std::vector<int> pol(descs.size() ? descs.size() : 1);
+    std::vector<double> stall(pol.size());
+    if (!descs.empty())
+      check(csw_cost_decide(&cost_model(), descs.data(), descs.size(), fwd_total, pol.data(), stall.data()),
+            "csw_cost_decide");
+    for (int i = 0; i < n; i++) policy[i] = 0;
+    for (size_t k = 0; k < cands.size(); k++) {
+      int p = pol[k];
+      if (all_zfp_where_allowed && descs[k].lossy_ok && descs[k].numel >= 1024) p = CSW_POLICY_ZFP;
+      policy[cands[k]] = p;
+      begin_stage[cands[k]] = consumer[cands[k]];
+    }
+    return policy;
   }
 
   csw_mgr* manager() const { return mgr_; }
@@ -109,16 +249,20 @@ class Execution {
     csw_mgr_get_stats(mgr_, &s);
     return s;
   }
+  void reset_stats() { csw_mgr_reset_stats(mgr_); }
 
   int index = -1;
-  long reclaimed = 0;  // tensors taken back before they had left the device
+  long reclaimed = 0;         // tensors taken back before they had left the device
+  long skipped_unsaved = 0;   // tensors nothing kept for backward: not copied out
+  long dropped = 0;           // policy 1: let go without a copy
+  long recomputed = 0;        // ... and rebuilt in backward
   std::vector<int> policy;
   std::vector<int> begin_stage;
   std::vector<Layer_type> types;
   int policy_ = 1;  // 1 CSWAP, 2 Capuchin, 3 vDNN, 4 SuperNeurons (Execution.h:420)
 
  private:
-  // One swapped-out storage, shared between the table below and the backward hook.
+  // One swapped-out or dropped storage, shared between the tables below and the backward hook.
   struct Swapped {
     Execution* exe = nullptr;
     c10::intrusive_ptr<c10::StorageImpl> storage;
@@ -127,10 +271,26 @@ class Execution {
     int order = -1;         // position among this step's swap-outs
     int policy = 0;
     bool restored = false;
+    bool started = false;   // the copy out (or the drop) has been issued
     at::DataPtr reading;    // the device block while the manager still reads it
+    // policy 1: how to rebuild the tensor
+    Producer producer;
+    torch::Tensor producer_input;
     ~Swapped() {
       if (ticket && exe && exe->mgr_) csw_ticket_release(exe->mgr_, ticket);
     }
+  };
+
+  // A tensor whose swap waits for its consumer to have run: only the consumer
+  // can still save it for backward, and an unsaved tensor is not worth a copy.
+  struct Deferred {
+    torch::Tensor t;
+    int pol;
+  };
+  // How an input of the running layer looked when pre() saw it.
+  struct Seen {
+    const c10::TensorImpl* impl;
+    size_t impl_refs, storage_refs;
   };
 
   struct RestoreHook : torch::autograd::FunctionPreHook {
@@ -140,6 +300,12 @@ class Execution {
       if (!s->restored) s->exe->restore(*s);
       return grads;
     }
+  };
+
+  struct ProfEntry {
+    at::cuda::CUDAEvent start{cudaEventDefault}, end{cudaEventDefault};
+    torch::Tensor zeros;  // fraction of zeros in the output, still on the device
+    LayerProfile p;
   };
 
   static void check(csw_status st, const char* what) {
@@ -157,12 +323,78 @@ class Execution {
            t.storage().data() != nullptr;  // not already swapped out through another view
   }
 
+  int effective_policy(int id, Layer_type layer_type) const {
+    int pol = policy[id];
+    if (pol == CSW_POLICY_DROP || (policy_ == 4 && layer_type != CONV))
+      return CSW_POLICY_DROP;  // Execution.h:243: SuperNeurons rebuilds the inputs of non-conv layers
+    if (layer_type == CONV && policy_ > 2) return CSW_POLICY_RAW;  // vDNN / SuperNeurons (Execution.h:70,248)
+    return pol;
+  }
+
   void maybe_swap_out(torch::Tensor& t, Layer_type layer_type) {
     const int id = id_of(t);
     if (id < 0 || id >= (int)begin_stage.size() || index != begin_stage[id] || !t.grad_fn()) return;
-    int pol = policy[id];
-    if (layer_type == CONV && policy_ > 2) pol = CSW_POLICY_RAW;  // vDNN / SuperNeurons baselines (Execution.h:70)
-    if ((pol != CSW_POLICY_RAW && pol != CSW_POLICY_SPARSE && pol != CSW_POLICY_ZFP) || !swappable(t)) return;
+    const int pol = effective_policy(id, layer_type);
+    if ((pol != CSW_POLICY_DROP && pol != CSW_POLICY_RAW && pol != CSW_POLICY_SPARSE && pol != CSW_POLICY_ZFP) ||
+        !swappable(t))
+      return;
+    {
+      auto seen = by_storage_.find(t.storage().unsafeGetStorageImpl());
+      if (seen != by_storage_.end() && !seen->second.expired()) return;
+    }
+    if (pol == CSW_POLICY_DROP && !producers_.count(t.unsafeGetTensorImpl()))
+      return;  // without its producer the tensor simply stays
+    // storage references beyond the tensor itself mean that its producer kept it for backward
+    // (a ReLU keeps its result): it will be needed again, so the copy out can start now and
+    // overlap with the consumer
+    if (t.storage().use_count() > 1) start_swap(t, pol);
+    else deferred_.push_back(Deferred{t, pol});
+  }
+
+  // Policy 1: nothing is copied; the storage is emptied after the consumer has
+  // run and the tensor rebuilt from its producer when backward asks for it.
+  void start_drop(const torch::Tensor& t) {
+    auto it = producers_.find(t.unsafeGetTensorImpl());
+    if (it == producers_.end()) return;
+    auto s = std::make_shared<Swapped>();
+    s->exe = this;
+    s->storage = c10::intrusive_ptr<c10::StorageImpl>::reclaim_copy(t.storage().unsafeGetStorageImpl());
+    s->nbytes = t.storage().nbytes();
+    s->policy = CSW_POLICY_DROP;
+    s->producer = it->second.first;
+    s->producer_input = it->second.second;
+    s->started = true;
+    by_storage_[s->storage.get()] = s;
+    pending_.push_back(s);
+    dropped++;
+  }
+
+  void note_input(const torch::Tensor& t) {
+    if (t.defined() && t.has_storage())
+      seen_.push_back(Seen{t.unsafeGetTensorImpl(), t.use_count(), t.storage().use_count()});
+  }
+
+  // Does anything hold `t` for backward now that its consumer has run?  Called
+  // from post() with the same handles in existence as in pre() (`own` counts the
+  // copies this class has made since).  Autograd adds a reference to the
+  // TensorImpl when a consumer saves its input and to the storage when a
+  // producer saves its own result.  The reference's drivers alias the tensor
+  // through `pre` and `x` when pre() runs and through `pre` alone when post()
+  // runs (vgg16-cifar10.cpp:219-226), so an unchanged count means one new
+  // holder.  With drivers that hold their handles differently the answer errs
+  // towards "held", which costs a copy, never correctness.
+  bool held_for_backward(const torch::Tensor& t, size_t own) const {
+    if (t.storage().use_count() > 1 + (by_storage_.count(t.storage().unsafeGetStorageImpl()) ? 1 : 0)) return true;
+    for (auto& sn : seen_)
+      if (sn.impl == t.unsafeGetTensorImpl()) return t.use_count() - own >= sn.impl_refs;
+    return true;
+  }
+
+  void start_swap(const torch::Tensor& t, int pol) {
+    if (pol == CSW_POLICY_DROP) {
+      start_drop(t);
+      return;
+    }
     auto s = std::make_shared<Swapped>();
     s->exe = this;
     s->storage = c10::intrusive_ptr<c10::StorageImpl>::reclaim_copy(t.storage().unsafeGetStorageImpl());
@@ -172,26 +404,70 @@ class Execution {
     if (st == CSW_ERR_NOMEM) return;  // pools exhausted: the tensor stays on the device
     check(st, "csw_swap_out");
     s->policy = pol;
+    s->started = true;
     s->order = (int)order_.size();
     order_.push_back(s);
+    by_storage_[s->storage.get()] = s;
     pending_.push_back(s);
   }
 
-  // The layer has run: give the result its id, let go of the swapped inputs'
-  // device blocks and arrange for their return before the result's backward.
-  void finish_layer(torch::Tensor& x) {
+  void begin_profile() {
+    if (!profile) return;
+    ProfEntry& e = prof_[index];
+    e.start.record(c10::cuda::getCurrentCUDAStream());
+  }
+
+  // The layer has run: give the result its id, decide the deferred swaps, let
+  // go of the swapped inputs' device blocks and arrange for their return before
+  // the result's backward.
+  void finish_layer(torch::Tensor* const* inputs, size_t n_in, torch::Tensor& x, Layer_type layer_type, bool isomit,
+                    Producer producer) {
     ids_[x.unsafeGetTensorImpl()] = index;
     auto fn = x.grad_fn();
+    if (profile) {
+      ProfEntry& e = prof_[index];
+      e.end.record(c10::cuda::getCurrentCUDAStream());
+      e.p.numel = (size_t)x.numel();
+      e.p.omit = isomit;
+      e.p.type = (int)layer_type;
+      e.p.float32 = x.scalar_type() == torch::kFloat32;
+      e.p.has_grad = (bool)fn;
+      e.p.recomputable = (bool)producer && n_in == 1;
+      if (x.is_cuda() && e.p.float32) e.zeros = (x.detach() == 0).to(torch::kFloat64).mean();
+      for (size_t i = 0; i < n_in; i++) {
+        const int tid = id_of(*inputs[i]);
+        e.p.inputs.push_back(tid);
+        // does anything hold this consumed tensor for backward now that its consumer has run?
+        if (tid >= 0 && inputs[i]->defined() && inputs[i]->is_cuda()) {
+          auto pit = prof_.find(tid);
+          if (pit != prof_.end()) pit->second.p.saved = held_for_backward(*inputs[i], 0);
+        }
+      }
+    }
+    for (auto& d : deferred_) {
+      const bool view = x.storage().unsafeGetStorageImpl() == d.t.storage().unsafeGetStorageImpl();
+      const bool saved = !view && held_for_backward(d.t, 1);
+      if (saved && fn) start_swap(d.t, d.pol);
+      else if (!saved && !view) skipped_unsaved++;
+    }
+    deferred_.clear();
+    // remember how to rebuild x, should it be dropped when its own consumer runs
+    if (producer && n_in == 1 && index < (int)policy.size() && (policy[index] == CSW_POLICY_DROP || policy_ == 4) &&
+        swappable(x) && x.storage().unsafeGetStorageImpl() != inputs[0]->storage().unsafeGetStorageImpl())
+      producers_[x.unsafeGetTensorImpl()] = {std::move(producer), *inputs[0]};
     for (auto& s : pending_) {
       // keep the tensor when nothing downstream will run backward through this
       // layer, or when the result is a view of it (same storage)
       if (!fn || x.storage().unsafeGetStorageImpl() == s->storage.get()) {
         s->restored = true;
+        if (s->policy == CSW_POLICY_DROP) dropped--;
         continue;
       }
-      // detach the device block from the storage; it is freed once the manager's streams are done with it
+      // detach the device block from the storage; a swapped block is freed once the
+      // manager's streams are done with it, a dropped one at once
       s->reading = s->storage->set_data_ptr(at::DataPtr(nullptr, s->storage->device()));
-      reading_.push_back(s);
+      if (s->policy == CSW_POLICY_DROP) s->reading.clear();
+      else reading_.push_back(s);
       fn->add_pre_hook(std::make_unique<RestoreHook>(s));
     }
     pending_.clear();
@@ -199,6 +475,10 @@ class Execution {
   }
 
   void restore(Swapped& s) {
+    if (s.policy == CSW_POLICY_DROP) {
+      rebuild(s);
+      return;
+    }
     // A losslessly swapped tensor that is needed again before the manager has
     // finished reading it never left the device: hand the block back as it is.
     // (A lossy one must come back as the decoded values whatever the timing.)
@@ -223,11 +503,37 @@ class Execution {
     for (int i = s.order - 1; i >= 0; i--) {
       auto p = order_[i].lock();
       if (p && !p->restored && p->ticket) {
-        csw_prefetch(mgr_, p->ticket);
+        int done = 1;
+        // a lossless ticket still on its way out may yet be taken back whole
+        if (p->policy != CSW_POLICY_ZFP) csw_swap_out_done(mgr_, p->ticket, &done);
+        if (done) csw_prefetch(mgr_, p->ticket);
         break;
       }
     }
     poll();
+  }
+
+  // Policy 1: run the producer again on its own input (swapped in or rebuilt
+  // first if that is gone too) and give the result's block to the storage.
+  void rebuild(Swapped& s) {
+    auto* in_storage = s.producer_input.storage().unsafeGetStorageImpl();
+    if (in_storage->data() == nullptr) {
+      auto it = by_storage_.find(in_storage);
+      std::shared_ptr<Swapped> in = it == by_storage_.end() ? nullptr : it->second.lock();
+      if (!in) throw std::runtime_error("cswap: the input of a dropped tensor's producer is gone");
+      if (!in->restored) restore(*in);
+    }
+    torch::Tensor out;
+    {
+      torch::NoGradGuard ng;
+      out = s.producer(s.producer_input).contiguous();
+    }
+    if (out.storage().nbytes() != s.nbytes || out.storage_offset() != 0)
+      throw std::runtime_error("cswap: recomputed activation does not match the dropped one");
+    auto* os = out.storage().unsafeGetStorageImpl();
+    s.storage->set_data_ptr_noswap(os->set_data_ptr(at::DataPtr(nullptr, os->device())));
+    s.restored = true;
+    recomputed++;
   }
 
   // free device blocks whose swap-out has finished reading them (never blocks)
@@ -247,14 +553,25 @@ class Execution {
       if (s->ticket) csw_swap_out_sync(mgr_, s->ticket);
     reading_.clear();
     pending_.clear();
+    deferred_.clear();
     order_.clear();
+    by_storage_.clear();
+    producers_.clear();
   }
 
   csw_mgr* mgr_ = nullptr;
+  unsigned maxbits_ = 512;
+  bool fitted_ = false;
+  csw_cost_model cost_{};
   std::unordered_map<const c10::TensorImpl*, int> ids_;
+  std::unordered_map<const c10::TensorImpl*, std::pair<Producer, torch::Tensor>> producers_;
+  std::unordered_map<const c10::StorageImpl*, std::weak_ptr<Swapped>> by_storage_;
   std::vector<std::shared_ptr<Swapped>> pending_;  // swap-outs started by the current pre()
+  std::vector<Deferred> deferred_;                 // swaps waiting for their consumer to have run
+  std::vector<Seen> seen_;                         // the running layer's inputs as pre() found them
   std::vector<std::shared_ptr<Swapped>> reading_;  // device blocks still being read
   std::vector<std::weak_ptr<Swapped>> order_;      // this step's swap-outs, in order
+  std::map<int, ProfEntry> prof_;
 };
 
 }  // namespace cswap

@@ -12,8 +12,40 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def test_cpp_driver_lossless_policies_keep_gradients():
     from cswap_b200 import build
-    exe = build.build_cpp_driver()
+    exe = build.build_cpp_driver(name="execution_driver")
     r = subprocess.run([exe], capture_output=True, text=True, timeout=300)
     print(r.stdout, r.stderr[-2000:])
     assert r.returncode == 0 and "PASS" in r.stdout
     assert "policy 2:" in r.stdout and "policy 3:" in r.stdout and "policy 6:" in r.stdout
+
+
+def test_cpp_vgg16_step_policies():
+    """VGG16 at batch 128 under the C++ Execution (tests/cpp/vgg16_step.cpp --check):
+    policies 1 / 2 / 3, the vDNN and SuperNeurons planners and the self-tuned
+    lossless table are bit-identical to the step without swapping, the profile
+    knows which activations nothing keeps, and policy 6 hands backward exactly
+    decode(encode(x))."""
+    from cswap_b200 import build
+    exe = build.build_cpp_driver(name="vgg16_step")
+    r = subprocess.run([exe, "--check"], capture_output=True, text=True, timeout=600)
+    print(r.stdout, r.stderr[-2000:])
+    assert r.returncode == 0 and "PASS" in r.stdout
+    for tag in ("policy 2 (raw)", "policy 3 (sparse)", "policy 1 (drop)", "policy_ 3 (vDNN)", "policy_ 4 (SuperNeurons)",
+                "self-tuned (lossless)", "policy 6 on id 2", "policy 6 on id 6"):
+        assert tag in r.stdout
+
+
+def test_cpp_vgg16_step_bench_line():
+    import json
+    from cswap_b200 import build
+    exe = build.build_cpp_driver(name="vgg16_step")
+    r = subprocess.run([exe, "--bench", "--steps", "3", "--warmup", "1"], capture_output=True, text=True, timeout=900)
+    print(r.stderr[-2000:])
+    assert r.returncode == 0
+    d = json.loads(r.stdout.strip().splitlines()[-1])
+    rows = d["rows"]
+    assert {"no_swap", "raw_swap", "reference_split_zfp8", "zfp8_everywhere", "self_tuned"} <= set(rows)
+    assert rows["no_swap"]["link_bytes_out"] == 0 and rows["raw_swap"]["link_bytes_out"] > 1e8
+    assert rows["zfp8_everywhere"]["link_bytes_out"] < 0.3 * rows["raw_swap"]["link_bytes_out"]
+    h = d["hidden_activation_bytes"]
+    assert set(h["per_policy"]) == {"raw", "compressed_reference_rule", "compressed_zfp8_everywhere"}

@@ -116,33 +116,40 @@ def test_known_answer_block(cs):
     assert [int(w) for w in s] == want
 
 
-def test_full_size_properties(cs, oracle):
-    """256 MiB tensor at rate 8: the stream of the whole equals the streams of
-    its parts (blocks are independent), sampled groups match the oracle, and
-    re-encoding the decoded tensor's decode is stable."""
+@pytest.mark.parametrize("mib,rate", [(256, 8), (256, 4), (256, 16), (512, 4), (512, 8), (512, 16)])
+def test_full_size_properties(cs, oracle, mib, rate):
+    """256 MiB and 512 MiB tensors (the top of the size sweep) at rates 4, 8 and
+    16: the stream of the whole equals the streams of its parts (blocks are
+    independent), sampled groups match the oracle, the decoded tensor equals
+    the oracle's decode of those groups and stays within the rate's error
+    bound, and a second trip through the codec stays within that bound."""
     import torch
-    n = 64 * 1024 * 1024
-    g = torch.Generator(device="cuda").manual_seed(7)
+    n = mib * 262144
+    maxbits = 64 * rate
+    bound = {4: 4.0, 8: 0.25, 16: 1.5e-3}[rate]
+    g = torch.Generator(device="cuda").manual_seed(7 + mib + rate)
     t = torch.tanh(torch.randn(n, device="cuda", generator=g))
     nz = n // 1024
-    whole = cs.zfp_compress(t, 512)
+    whole = cs.zfp_compress(t, maxbits)
+    assert whole.numel() == n * rate // 8
     part = 4 * 1024 * 1024
-    for k in range(0, n, part * 4):  # every 4th 16 MiB piece
-        piece = cs.zfp_compress(t[k:k + part].contiguous(), 512)
-        assert torch.equal(piece, whole[k:k + part])  # rate 8: one stream byte per value
-    rng = np.random.default_rng(0)
-    for z0 in rng.integers(0, nz - 16, 24):
-        z0 = int(z0) & ~3
+    for k in range(0, n, part * 8):  # every 8th 16 MiB piece
+        piece = cs.zfp_compress(t[k:k + part].contiguous(), maxbits)
+        assert torch.equal(piece, whole[k * rate // 8:(k + part) * rate // 8])
+    back = cs.zfp_decompress(whole, n, maxbits)
+    rng = np.random.default_rng(mib + rate)
+    picks = [0, nz - 16] + [int(z) & ~3 for z in rng.integers(0, nz - 16, 14)]
+    for z0 in picks:
         a = t[z0 * 1024:(z0 + 16) * 1024].cpu().numpy()
-        ref = oracle.zfp_encode(a, 32, 32, 16, 512)
-        got = whole[z0 * 1024:(z0 + 16) * 1024].cpu().numpy().view(np.uint64)
+        ref = oracle.zfp_encode(a, 32, 32, 16, maxbits)
+        got = whole[z0 * 128 * rate:(z0 + 16) * 128 * rate].cpu().numpy().view(np.uint64)
         assert np.array_equal(got, ref)
-    back = cs.zfp_decompress(whole, n, 512)
-    err = (back - t)
-    assert float(err.abs().max()) < 0.25
-    again = cs.zfp_decompress(cs.zfp_compress(back, 512), n, 512)
+        ref_back = oracle.zfp_decode(ref, 32, 32, 16, maxbits)
+        assert np.array_equal(back[z0 * 1024:(z0 + 16) * 1024].cpu().numpy().view(np.uint32), ref_back.view(np.uint32))
+    assert float((back - t).abs().max()) < bound
+    again = cs.zfp_decompress(cs.zfp_compress(back, maxbits), n, maxbits)
     # a second trip through the codec moves values by at most the first trip's error bound
-    assert float((again - back).abs().max()) < 0.25
+    assert float((again - back).abs().max()) < bound
     assert cs.lib().csw_device_status(None) == 0
 
 
