@@ -487,6 +487,34 @@ def hidden_bytes_sweep(W, cs, torch, model, mgr, make_batch, prof, policy_of, t_
     return {"candidates": len(ids), "hidden_activation_bytes": hidden, "curve": curve}
 
 
+def vgg16_cpp_block(torch, dev, world, rank, local):
+    """The swapped VGG16 step through the C++ host side (cswap::Execution over
+    libtorch, tests/cpp/vgg16_step.cpp, the driver laid out like the
+    reference's vgg16-cifar10.cpp): every rank launches the binary on its own
+    GPU behind one barrier, so the ranks share the host link while they run.
+    Rank 0's line is reported, with each row's step time replaced by the
+    slowest rank's."""
+    import subprocess
+    import torch.distributed as dist
+    exe = os.path.join(ROOT, "tests", "cpp", "vgg16_step")
+    if not os.path.exists(exe):
+        return {"unavailable": "tests/cpp/vgg16_step has not been built (python -m cswap_b200.build --cpp)"}
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    r = subprocess.run([exe, "--bench", "--device", str(local), "--seed", str(1 + rank)], capture_output=True,
+                       text=True, timeout=900)
+    if r.returncode != 0:
+        return {"unavailable": f"vgg16_step exited {r.returncode}: {r.stderr[-300:]}"}
+    d = json.loads(r.stdout.strip().splitlines()[-1])
+    names = sorted(d["rows"])
+    worst = max_over_ranks([d["rows"][k]["ms_per_step_median"] for k in names], dev)
+    for k, w in zip(names, worst):
+        d["rows"][k]["ms_per_step_median_slowest_rank"] = w
+    d["ranks_running"] = world
+    return d
+
+
 def vgg16_block(args, cs, torch, dev, world, rank):
     """The swapped VGG16 training step (batch 128, 3x32x32 synthetic inputs,
     CSWAP+/vgg16-cifar10.cpp:135-245) on every rank at once: step time, link
@@ -739,7 +767,8 @@ def main():
         e2e["link_floor_ms_per_step"] = t_floor * 1e3
         e2e["fraction_of_link_ceiling"] = t_floor / t_e2e
         if not args.no_vgg:
-            extra["vgg16"] = vgg16_block(args, cs, torch, dev, world, rank)
+            extra["vgg16"] = vgg16_cpp_block(torch, dev, world, rank, local)
+            extra["vgg16_python_engine"] = vgg16_block(args, cs, torch, dev, world, rank)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:

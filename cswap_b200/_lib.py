@@ -134,6 +134,15 @@ SIGNATURES = {
     "GPUdecompression": (None, [_P, _P, _I, _I, _P, _P, _I, _I]),
     "cuda_compress": (_SZ, [C.POINTER(ZfpStream), C.POINTER(ZfpField)]),
     "cuda_decompress": (None, [C.POINTER(ZfpStream), C.POINTER(ZfpField)]),
+    "csw_set_device_allocator": (None, [_P, _P]),
+}
+
+# entry points with C++ linkage (the wrappers the reference's Execution calls,
+# CSWAP+/Execution.h:63,113): declared name -> (exported symbol, restype, argtypes)
+CXX_SIGNATURES = {
+    "setRatio": ("_Z8setRatioi", None, [_I]),
+    "compress": ("_Z8compressPvmRm", _P, [_P, _SZ, C.POINTER(_SZ)]),
+    "decompress": ("_Z10decompressPvmS_m", None, [_P, _SZ, _P, _SZ]),
 }
 
 _lib = None
@@ -152,6 +161,11 @@ def lib():
             fn = getattr(L, name)
             fn.restype = res
             fn.argtypes = args
+        for name, (symbol, res, args) in CXX_SIGNATURES.items():
+            fn = getattr(L, symbol)
+            fn.restype = res
+            fn.argtypes = args
+            setattr(L, "cxx_" + name, fn)
         _lib = L
     return _lib
 

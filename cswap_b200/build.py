@@ -90,4 +90,7 @@ def build_cpp_drivers(force: bool = False):
 
 
 if __name__ == "__main__":
+    if "--cpp" in sys.argv:
+        print(build_cpp_drivers(force="--force" in sys.argv))
+        sys.exit(0)
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -100,9 +100,13 @@ csw_status csw_cost_fit(csw_mgr* m, csw_cost_model* model) {
   cudaEvent_t e0 = nullptr, e1 = nullptr;
   csw_sparse_layout L;
   csw_sparse_layout_of(nmax, &L);
+  // the compressed-side buffer holds the larger of the sparse bound and the ZFP stream at this rate
+  size_t c_bytes = L.bound, z_bytes = 0;
+  csw_zfp_max_bytes(32, 32, nmax / 1024, mb, &z_bytes);
+  if (z_bytes > c_bytes) c_bytes = z_bytes;
   cudaError_t e = cudaMalloc(&d_x, nmax * 4);
   if (e == cudaSuccess) e = cudaMalloc(&d_y, nmax * 4);
-  if (e == cudaSuccess) e = cudaMalloc(&d_c, L.bound);
+  if (e == cudaSuccess) e = cudaMalloc(&d_c, c_bytes);
   if (e == cudaSuccess) e = cudaMalloc(&d_nnz, 4);
   if (e == cudaSuccess) e = cudaHostAlloc(&h, nmax * 4, cudaHostAllocDefault);
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking);
@@ -121,7 +125,7 @@ csw_status csw_cost_fit(csw_mgr* m, csw_cost_model* model) {
     csw_zfp_max_bytes(32, 32, nz, mb, &zb);
     double t = 0;
     xb.push_back((double)n * 4);
-    st = time_op(s, e0, e1, 5, [&] { return csw_zfp_compress(d_x, 32, 32, nz, mb, d_c, L.bound, nullptr, s); }, &t);
+    st = time_op(s, e0, e1, 5, [&] { return csw_zfp_compress(d_x, 32, 32, nz, mb, d_c, c_bytes, nullptr, s); }, &t);
     t_ze.push_back(t);
     if (st == CSW_OK)
       st = time_op(s, e0, e1, 5, [&] { return csw_zfp_decompress(d_c, zb, 32, 32, nz, mb, d_y, s); }, &t);

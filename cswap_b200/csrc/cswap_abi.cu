@@ -107,7 +107,12 @@ csw_status csw_device_status(csw_stream_t stream) {
 csw_status csw_zfp_max_bytes(size_t nx, size_t ny, size_t nz, unsigned maxbits, size_t* bytes) {
   if (!bytes || !valid_maxbits(maxbits)) return CSW_ERR_ARG;
   if (nx == 0 || (ny == 0 && nz != 0)) return CSW_ERR_ARG;
-  *bytes = stream_bytes(make_geom(nx, ny, nz, 0, 0, 0), maxbits);
+  if (nx > 0xfffffffcu || ny > 0xfffffffcu || nz > 0xfffffffcu) return CSW_ERR_ARG;  // extents are 32-bit inside
+  const FieldGeom g = make_geom(nx, ny, nz, 0, 0, 0);
+  // blocks * maxbits must not wrap a 64-bit count of bits
+  const unsigned __int128 bits = (unsigned __int128)g.bx * g.by * g.bz * maxbits;
+  if (bits > ((unsigned __int128)1 << 62)) return CSW_ERR_ARG;
+  *bytes = stream_bytes(g, maxbits);
   return CSW_OK;
 }
 
@@ -373,7 +378,13 @@ bool pipelined_host_call(bool compress, const csw_zfp_field* f, void* h_stream, 
       if (e != cudaSuccess) break;
       st = csw_zfp_compress(reinterpret_cast<const float*>(d_field + foff), f->nx, f->ny, nzc, maxbits,
                             d_stream + soff, slen, nullptr, g_pipe.work);
-      if (st != CSW_OK) return true;
+      if (st != CSW_OK) {
+        // work of earlier chunks is still queued on the three streams and the staging buffers are shared
+        cudaStreamSynchronize(g_pipe.in);
+        cudaStreamSynchronize(g_pipe.work);
+        cudaStreamSynchronize(g_pipe.out);
+        return true;
+      }
       e = cudaEventRecord(g_pipe.coded[c], g_pipe.work);
       if (e == cudaSuccess) e = cudaStreamWaitEvent(g_pipe.out, g_pipe.coded[c], 0);
       if (e == cudaSuccess) e = cudaMemcpyAsync(hs + soff, d_stream + soff, slen, cudaMemcpyDeviceToHost, g_pipe.out);
@@ -384,7 +395,13 @@ bool pipelined_host_call(bool compress, const csw_zfp_field* f, void* h_stream, 
       if (e != cudaSuccess) break;
       st = csw_zfp_decompress(d_stream + soff, slen, f->nx, f->ny, nzc, maxbits,
                               reinterpret_cast<float*>(d_field + foff), g_pipe.work);
-      if (st != CSW_OK) return true;
+      if (st != CSW_OK) {
+        // work of earlier chunks is still queued on the three streams and the staging buffers are shared
+        cudaStreamSynchronize(g_pipe.in);
+        cudaStreamSynchronize(g_pipe.work);
+        cudaStreamSynchronize(g_pipe.out);
+        return true;
+      }
       e = cudaEventRecord(g_pipe.coded[c], g_pipe.work);
       if (e == cudaSuccess) e = cudaStreamWaitEvent(g_pipe.out, g_pipe.coded[c], 0);
       if (e == cudaSuccess) e = cudaMemcpyAsync(h_field + foff, d_field + foff, flen, cudaMemcpyDeviceToHost, g_pipe.out);
@@ -504,3 +521,90 @@ void cuda_decompress(csw_zfp_stream* zs, csw_zfp_field* f) {
 }
 
 }  // extern "C"
+
+
+// ---- the wrappers the reference's Execution calls (Execution.h:63,113,296) ----------
+namespace {
+std::mutex g_wrap_mu;
+unsigned g_ratio_maxbits = 512;
+csw_alloc_fn g_alloc = nullptr;
+csw_free_fn g_free = nullptr;
+
+void* wrap_alloc(size_t bytes) {
+  if (g_alloc) return g_alloc(bytes);
+  void* p = nullptr;
+  return cudaMalloc(&p, bytes) == cudaSuccess ? p : nullptr;
+}
+void wrap_free(void* p) {
+  if (!p) return;
+  if (g_free) g_free(p);
+  else cudaFree(p);
+}
+// stream bytes and total bytes (stream + the values past the last whole slab)
+bool wrap_geometry(size_t numel, unsigned maxbits, size_t* nz, size_t* zbytes, size_t* bytes) {
+  *nz = numel / 1024;
+  *zbytes = 0;
+  if (*nz && csw_zfp_max_bytes(32, 32, *nz, maxbits, zbytes) != CSW_OK) return false;
+  *bytes = *zbytes + (numel % 1024) * sizeof(float);
+  return true;
+}
+}  // namespace
+
+extern "C" void csw_set_device_allocator(csw_alloc_fn alloc, csw_free_fn release) {
+  std::lock_guard<std::mutex> lk(g_wrap_mu);
+  g_alloc = alloc && release ? alloc : nullptr;
+  g_free = alloc && release ? release : nullptr;
+}
+
+void setRatio(int maxbits) {
+  size_t probe;
+  std::lock_guard<std::mutex> lk(g_wrap_mu);
+  if (maxbits > 0 && csw_zfp_max_bytes(32, 32, 4, (unsigned)maxbits, &probe) == CSW_OK) g_ratio_maxbits = (unsigned)maxbits;
+  else legacy_report("setRatio", cudaErrorInvalidValue);
+}
+
+void* compress(void* dev_ptr, size_t numel, size_t& out_bytes) {
+  out_bytes = 0;
+  unsigned maxbits;
+  {
+    std::lock_guard<std::mutex> lk(g_wrap_mu);
+    maxbits = g_ratio_maxbits;
+  }
+  size_t nz, zbytes, bytes;
+  if (!dev_ptr || !numel || !wrap_geometry(numel, maxbits, &nz, &zbytes, &bytes)) return nullptr;
+  void* buf = wrap_alloc(bytes);
+  if (!buf) return nullptr;
+  csw_status st = CSW_OK;
+  if (nz) st = csw_zfp_compress(static_cast<const float*>(dev_ptr), 32, 32, nz, maxbits, buf, zbytes, nullptr, nullptr);
+  cudaError_t e = cudaSuccess;
+  if (st == CSW_OK && bytes > zbytes)
+    e = cudaMemcpyAsync(static_cast<char*>(buf) + zbytes, static_cast<const float*>(dev_ptr) + nz * 1024, bytes - zbytes,
+                        cudaMemcpyDeviceToDevice, nullptr);
+  if (st != CSW_OK || e != cudaSuccess) {
+    legacy_report("compress", e != cudaSuccess ? e : cudaErrorUnknown);
+    wrap_free(buf);
+    return nullptr;
+  }
+  out_bytes = bytes;
+  return buf;
+}
+
+void decompress(void* dev_buf, size_t bytes, void* dev_dst, size_t numel) {
+  unsigned maxbits;
+  {
+    std::lock_guard<std::mutex> lk(g_wrap_mu);
+    maxbits = g_ratio_maxbits;
+  }
+  size_t nz, zbytes, need;
+  if (!dev_buf || !dev_dst || !numel || !wrap_geometry(numel, maxbits, &nz, &zbytes, &need) || bytes < need) {
+    legacy_report("decompress", cudaErrorInvalidValue);
+    return;
+  }
+  csw_status st = CSW_OK;
+  if (nz) st = csw_zfp_decompress(dev_buf, zbytes, 32, 32, nz, maxbits, static_cast<float*>(dev_dst), nullptr);
+  cudaError_t e = cudaSuccess;
+  if (st == CSW_OK && need > zbytes)
+    e = cudaMemcpyAsync(static_cast<float*>(dev_dst) + nz * 1024, static_cast<const char*>(dev_buf) + zbytes,
+                        need - zbytes, cudaMemcpyDeviceToDevice, nullptr);
+  if (st != CSW_OK || e != cudaSuccess) legacy_report("decompress", e != cudaSuccess ? e : cudaErrorUnknown);
+}

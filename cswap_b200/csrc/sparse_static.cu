@@ -7,7 +7,9 @@
 // would stall other streams, or an embedding with a fixed memory budget handed
 // over at start-up.  For them the per-tile counters of the compressor live in
 // a fixed array inside the library image instead of anywhere that has to be
-// obtained at run time.
+// obtained at run time.  (The driver places that array, and the kernels, on a
+// device when the library's code is first used there; a warm-up call at
+// start-up gets that over with while memory is still available.)
 #include <cuda_runtime.h>
 
 #include <cstdint>

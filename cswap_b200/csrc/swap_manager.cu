@@ -387,6 +387,11 @@ csw_status csw_swap_out(csw_mgr* m, const float* d_ptr, size_t numel, int policy
   const size_t stage_need = policy == CSW_POLICY_RAW ? 0 : host_need;
 
   auto fail = [&](csw_status st) {
+    // codec or copy work may already be queued on the manager's streams: let it finish
+    // before the memory it touches goes back to the pools
+    cudaStreamSynchronize(m->s_codec);
+    cudaStreamSynchronize(m->s_d2h);
+    cudaGetLastError();
     if (t->host) m->pinned.release(t->host, t->host_cap);
     free_stage(m, t);
     if (t->nnz_slot >= 0) m->free_slots.push_back(t->nnz_slot);
@@ -648,6 +653,8 @@ csw_status csw_blob_info(const void* blob, size_t bytes, csw_blob_header* header
   csw_blob_header h;
   std::memcpy(&h, blob, sizeof h);
   if (h.magic != CSW_BLOB_MAGIC || h.version != CSW_BLOB_VERSION || h.numel == 0) return CSW_ERR_ARG;
+  // element counts beyond 2^40 (4 TiB of floats) cannot be real and would let the size arithmetic below wrap
+  if (h.numel > ((uint64_t)1 << 40)) return CSW_ERR_ARG;
   if (bytes - sizeof h < h.payload_bytes) return CSW_ERR_SIZE;
   const unsigned char* payload = static_cast<const unsigned char*>(blob) + sizeof h;
   if (h.policy == CSW_POLICY_RAW) {

@@ -539,8 +539,9 @@ CSW_HD void encode_block(const float (&f)[1 << (2 * DIMS)], int maxbits, WordSin
 struct PipeConsts {
   int one, mone;         // 1, -1
   uint32_t p1, p2, p4;   // 1 << 1, 1 << 2, 1 << 4
+  uint32_t nb;           // 0xaaaaaaaa, the negabinary mask
 };
-CSW_HD PipeConsts pipe_consts() { return PipeConsts{1, -1, 2u, 4u, 16u}; }
+CSW_HD PipeConsts pipe_consts() { return PipeConsts{1, -1, 2u, 4u, 16u, 0xaaaaaaaau}; }
 
 CSW_HD int imad(int a, int b, int c) {
 #if defined(__CUDA_ARCH__)
@@ -601,6 +602,9 @@ CSW_HD void planes_of_byte_bal(const uint32_t (&u)[64], uint32_t sel, uint32_t (
     p[j] = byte_perm(t0, t1, 0x5410);
   }
   transpose8_bal(p, k);
+  // the coefficients came in as v + 0xaaaaaaaa; the xor half of the negabinary
+  // map flips every odd bit, i.e. it complements the odd planes
+  p[1] = ~p[1]; p[3] = ~p[3]; p[5] = ~p[5]; p[7] = ~p[7];
 }
 
 constexpr int STAGE_SPARE_ROWS = 2;  // words a write may run past the block's last word
@@ -616,6 +620,12 @@ CSW_HD void stage_put64(Stage& st, int off, uint32_t lo, uint32_t hi) {
   st.or_word(w, lo << s);
   st.or_word(w + 1, funnel_l(lo, hi, s));
   st.or_word(w + 2, funnel_l(hi, 0u, s));
+}
+
+template <int... I>
+CSW_HD void fwd_order3_add(const int (&v)[64], uint32_t (&u)[64], uint32_t nb, int one,
+                           std::integer_sequence<int, I...>) {
+  ((u[I] = umad((uint32_t)v[PermAt<3, I>::v], (uint32_t)one, nb)), ...);
 }
 
 template <class Stage>
@@ -635,7 +645,7 @@ CSW_HD void encode_block3_staged(const float (&f)[64], int maxbits, Stage& st, c
   }
   fwd_xform3_bal(v, kc);
   uint32_t u[64];
-  fwd_order<3>(v, u, std::make_integer_sequence<int, 64>{});
+  fwd_order3_add(v, u, kc.nb, kc.one, std::make_integer_sequence<int, 64>{});
 
   SigState sg;
   sg.set(0);
@@ -858,8 +868,14 @@ CSW_HD void rol64(uint32_t& l, uint32_t& h, int r) {
   h = funnel_l(a, b, r);
 }
 
+template <int... I>
+CSW_HD void inv_order3_sub(const uint32_t (&u)[64], int (&v)[64], uint32_t nb, int mone,
+                           std::integer_sequence<int, I...>) {
+  ((v[PermAt<3, I>::v] = imad((int)nb, mone, (int)u[I])), ...);  // u - 0xaaaaaaaa on the multiply-add pipe
+}
 template <class WordSrc>
-CSW_HD void decode_block3_pos(const WordSrc& src, int maxbits, float (&f)[64], const uint32_t* dec_lut) {
+CSW_HD void decode_block3_pos(const WordSrc& src, int maxbits, float (&f)[64], const uint32_t* dec_lut,
+                              const PipeConsts& kc) {
   const uint32_t head = src.word(0);
   if (!(head & 1u)) {  // zero block
 #pragma unroll
@@ -869,8 +885,9 @@ CSW_HD void decode_block3_pos(const WordSrc& src, int maxbits, float (&f)[64], c
   const uint32_t e = (head >> 1) & 0xffu;
   int pos = 9, n = 0;
   uint32_t u[64];
+  // u holds coefficient ^ 0xaaaaaaaa throughout (planes never decoded are zero, i.e. 0xaa bytes)
 #pragma unroll
-  for (int i = 0; i < 64; i++) u[i] = 0;
+  for (int i = 0; i < 64; i++) u[i] = 0xaaaaaaaau;
   for (int c = 3; c >= 0; c--) {
     uint32_t lo[8], hi[8];
 #pragma unroll
@@ -925,12 +942,18 @@ CSW_HD void decode_block3_pos(const WordSrc& src, int maxbits, float (&f)[64], c
     }
     const uint32_t sel0 = (0x3210u & ~(0xfu << (4 * c))) | (4u << (4 * c));
     const uint32_t step = 1u << (4 * c);
+    // the xor half of the inverse negabinary map, applied to planes instead of coefficients
+#pragma unroll
+    for (int k = 1; k < 8; k += 2) {
+      lo[k] = ~lo[k];
+      hi[k] = ~hi[k];
+    }
     bytes_from_planes<0>(lo, sel0, step, u);
     bytes_from_planes<1>(hi, sel0, step, u);
     if (pos >= maxbits) break;
   }
   int v[64];
-  inv_order<3>(u, v, std::make_integer_sequence<int, 64>{});
+  inv_order3_sub(u, v, kc.nb, kc.mone, std::make_integer_sequence<int, 64>{});
   inv_xform<3>(v);
   const float w = dequant_scale(e);
 #pragma unroll

@@ -148,7 +148,8 @@ static_assert(DEC_LUT_SIZE % (4 * kThreads) == 0, "table copy assumes whole 128-
 // area, parses them by bit position and stores the rebuilt 4x4x4 block with
 // sixteen 128-bit stores.  The only barrier is the one after the table copy.
 __global__ void __launch_bounds__(kThreads, kDecCtasPerSm)
-zfp_decode_slab_kernel(const uint32_t* __restrict__ in, float* __restrict__ out, uint32_t nz, int maxbits) {
+zfp_decode_slab_kernel(const uint32_t* __restrict__ in, float* __restrict__ out, uint32_t nz, int maxbits,
+                       const PipeConsts kc) {
   extern __shared__ __align__(16) uint32_t smem_words[];
   const int nwords = maxbits >> 5;
   uint32_t* stage = smem_words;
@@ -183,7 +184,7 @@ zfp_decode_slab_kernel(const uint32_t* __restrict__ in, float* __restrict__ out,
 
   float f[64];
   StageWords source{col};
-  decode_block3_pos(source, maxbits, f, lut);
+  decode_block3_pos(source, maxbits, f, lut, kc);
   // eight neighbouring lanes cover one 128-byte row segment, so every store
   // instruction of a warp writes four full lines: no staging of the output
   const int vz = nz - zt < 4 ? (int)(nz - zt) : 4;
@@ -328,7 +329,7 @@ cudaError_t zfp_decode_launch(const FieldGeom& g, const void* in, float* out, in
     if (e != cudaSuccess) return e;
     const uint32_t ngroups = (g.nz + kGroupSlabs - 1) / kGroupSlabs;
     zfp_decode_slab_kernel<<<ngroups, kThreads, smem, stream>>>(reinterpret_cast<const uint32_t*>(in), out, g.nz,
-                                                               maxbits);
+                                                               maxbits, pipe_consts());
     return cudaGetLastError();
   }
   const unsigned grid = (unsigned)((nblocks + 127) / 128);

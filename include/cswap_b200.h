@@ -149,9 +149,13 @@ csw_status csw_sparse_compress_onepass(const float* d_in, size_t n, void* d_out,
  *
  *  - n may be at most CSW_SPARSE_STATIC_MAX_ELEMS; larger inputs return
  *    CSW_ERR_LIMIT and launch nothing.
- *  - The first call on each device looks up the array's device address (a
- *    runtime query, not an allocation); make that first call outside any
- *    stream capture.
+ *  - The first call on each device looks up the array's device address.  With
+ *    the CUDA runtime's default lazy loading that first lookup (or launch) is
+ *    also when the driver loads the library's kernels and the array itself
+ *    onto the device, which does take device memory and can fail when none is
+ *    left.  So make one warm-up call per device (n = 0 is enough) at start-up,
+ *    outside any stream capture and before memory is tight; later calls on
+ *    that device touch no allocator of any kind.
  *  - All calls share the one array: two calls whose kernels may run at the same
  *    time on the same GPU (different streams, no ordering between them) race
  *    and corrupt each other's output.  Calls ordered on one stream, or by

@@ -78,6 +78,36 @@ size_t cuda_compress(csw_zfp_stream* stream, const csw_zfp_field* field);
 /* Inverse (cuZFP.cu:440-532). */
 void cuda_decompress(csw_zfp_stream* stream, csw_zfp_field* field);
 
+/* ---- the wrappers the reference's Execution calls -------------------------- */
+/* Device memory for buffers the library hands to its caller (compress below).
+ * Defaults to cudaMalloc / cudaFree; a libtorch program passes the caching
+ * allocator's raw_alloc / raw_delete so that the caller can free the buffer
+ * the way the reference does (Execution.h:296).  NULL restores the default. */
+typedef void* (*csw_alloc_fn)(size_t bytes);
+typedef void (*csw_free_fn)(void* p);
+void csw_set_device_allocator(csw_alloc_fn alloc, csw_free_fn release);
+
+#ifdef __cplusplus
+}
+
+/* C++ linkage, as in the reference's modified PyTorch (the definitions are not
+ * part of the reference tree; only the call sites are):
+ *   setRatio(int)            CSWAP+/Execution.h:63   bits per zfp block for later compress() calls
+ *   compress(ptr, n, bytes)  CSWAP+/Execution.h:113  ZFP-compress n floats at dev_ptr on the legacy
+ *                            default stream into a new device buffer (allocated through the
+ *                            allocator set above, freed by the caller); out_bytes receives its
+ *                            size.  The tensor is viewed 32 x 32 x n/1024; values past the last
+ *                            whole slab follow the stream as they are.  NULL (out_bytes 0) on failure.
+ *   decompress(buf, bytes, dst, n)  the inverse, for the swap-in half the reference keeps in its
+ *                            engine: rebuilds n floats at dev_dst from a buffer made by compress()
+ *                            at the current ratio. */
+void setRatio(int maxbits);
+void* compress(void* dev_ptr, size_t numel, size_t& out_bytes);
+void decompress(void* dev_buf, size_t bytes, void* dev_dst, size_t numel);
+
+extern "C" {
+#endif
+
 #ifdef __cplusplus
 }
 #endif

@@ -98,7 +98,7 @@ void core_decode_pos(const uint32_t* in, size_t nx, size_t ny, size_t nz, int ma
   for (size_t b = 0; b < nb; b++) {
     float q[64];
     PadSource s{in + b * nw, nw};
-    csw::decode_block3_pos(s, maxbits, q, lut.data());
+    csw::decode_block3_pos(s, maxbits, q, lut.data(), csw::pipe_consts());
     csw::scatter_block<3>(g, out, b, q);
   }
 }

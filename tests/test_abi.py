@@ -20,18 +20,22 @@ def L():
 def _declared(header):
     text = open(os.path.join(ROOT, "include", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    text = re.sub(r"^\s*typedef[^;{]*\([^;]*;", "", text, flags=re.M)  # function-pointer typedefs declare no symbol
     names = re.findall(r"^\s*(?:const\s+)?[A-Za-z_][\w\s\*]*?\b(\w+)\s*\([^;{]*\)\s*;", text, flags=re.M)
     return sorted(set(n for n in names if n not in ("defined",)))
 
 
 def test_every_declared_symbol_is_exported_and_bound(L):
-    from cswap_b200._lib import SIGNATURES
+    from cswap_b200._lib import CXX_SIGNATURES, SIGNATURES
     declared = _declared("cswap_b200.h") + _declared("cswap_compat.h")
-    assert len(declared) >= 37
+    assert len(declared) >= 41
     for name in declared:
+        if name in CXX_SIGNATURES:  # C++ linkage: exported under its mangled name
+            assert hasattr(L, CXX_SIGNATURES[name][0]), f"{name} is declared in include/ but not exported"
+            continue
         assert hasattr(L, name), f"{name} is declared in include/ but not exported"
         assert name in SIGNATURES, f"{name} has no ctypes signature"
-    assert sorted(SIGNATURES) == sorted(set(declared))
+    assert sorted(list(SIGNATURES) + list(CXX_SIGNATURES)) == sorted(set(declared))
 
 
 def test_sizing_and_layout_without_a_device(L):

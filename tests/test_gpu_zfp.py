@@ -278,3 +278,52 @@ def test_large_host_call_is_pipelined_and_exact(cs):
     L.cuda_decompress(C.byref(zs2), C.byref(fld2))
     assert bs2.ptr == sp + nbytes
     assert torch.equal(h_out, want_back.cpu())
+
+
+def test_fork_wrappers_compress_set_ratio(cs, oracle):
+    """setRatio / compress / decompress, the wrappers the reference's Execution
+    calls (CSWAP+/Execution.h:63,113): the buffer compress() returns holds the
+    oracle's stream of the 32 x 32 x n/1024 view followed by the values past
+    the last whole slab, and it comes from the allocator the caller supplied."""
+    import torch
+    L = cs.lib()
+    held = {}
+
+    @C.CFUNCTYPE(C.c_void_p, C.c_size_t)
+    def alloc(nbytes):
+        t = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+        held[t.data_ptr()] = t
+        return t.data_ptr()
+
+    @C.CFUNCTYPE(None, C.c_void_p)
+    def release(p):
+        held.pop(p, None)
+
+    L.csw_set_device_allocator(C.cast(alloc, C.c_void_p), C.cast(release, C.c_void_p))
+    try:
+        n = 1024 * 20 + 300
+        a = util.tanh_normal(n, 21)
+        t = torch.from_numpy(a).cuda()
+        torch.cuda.synchronize()
+        for maxbits in (128, 512):
+            L.cxx_setRatio(maxbits)
+            nbytes = C.c_size_t()
+            buf = L.cxx_compress(t.data_ptr(), n, C.byref(nbytes))
+            assert buf in held and nbytes.value == 20 * 128 * maxbits // 8 + 300 * 4
+            torch.cuda.synchronize()
+            g = held[buf].cpu().numpy()[:nbytes.value]
+            zb = nbytes.value - 1200
+            ref = oracle.zfp_encode(a[:20480], 32, 32, 20, maxbits)
+            assert np.array_equal(g[:zb].view(np.uint64), ref)
+            assert np.array_equal(g[zb:].view(np.float32), a[20480:])
+            back = torch.zeros(n, device="cuda")
+            torch.cuda.synchronize()
+            L.cxx_decompress(buf, nbytes.value, back.data_ptr(), n)
+            torch.cuda.synchronize()
+            want = np.concatenate([oracle.zfp_decode(ref, 32, 32, 20, maxbits), a[20480:]])
+            assert np.array_equal(back.cpu().numpy().view(np.uint32), want.view(np.uint32))
+            release(buf)
+        assert not held
+    finally:
+        L.cxx_setRatio(512)
+        L.csw_set_device_allocator(None, None)

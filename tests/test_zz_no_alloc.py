@@ -12,12 +12,13 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-def _packed(cs, fn, t, n):
+def _packed(cs, fn, t, n, out=None, nnz=None):
     """Run one compress entry point; return (tile_off, bitmap, values, nnz) as numpy."""
     import torch
     L = cs.sparse_layout(n)
-    out = torch.zeros(L.bound, dtype=torch.uint8, device="cuda")
-    nnz = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    if out is None:
+        out = torch.zeros(L.bound, dtype=torch.uint8, device="cuda")
+        nnz = torch.full((1,), -1, dtype=torch.int32, device="cuda")
     st = fn(t.data_ptr(), n, out.data_ptr(), L.bound, nnz.data_ptr(), torch.cuda.current_stream().cuda_stream)
     assert st == 0
     torch.cuda.synchronize()
@@ -46,6 +47,20 @@ def test_static_scratch_entry_point_matches_the_allocating_one():
             assert np.array_equal(g, w)  # bit for bit
         back = cs.sparse_decompress(_repack(cs, got, n), n)
         assert np.array_equal(back.cpu().numpy().view(np.uint32), a.view(np.uint32))
+    out_keep = torch.zeros(cs.sparse_layout(n).bound, dtype=torch.uint8, device="cuda")
+    nnz_keep = torch.zeros(1, dtype=torch.int32, device="cuda")
+    # a warmed call takes no device memory: the driver's free-memory figure does not move
+    free0 = torch.cuda.mem_get_info()[0]
+    got = _packed(cs, lib.csw_sparse_compress_static, t, n, out=out_keep, nnz=nnz_keep)
+    assert torch.cuda.mem_get_info()[0] == free0
+    # n = 0 (the warm-up form) is accepted and leaves a zero count
+    z = torch.full((1,), 5, dtype=torch.int32, device="cuda")
+    assert lib.csw_sparse_compress_static(None, 0, out_keep.data_ptr(), out_keep.numel(), z.data_ptr(), None) == 0
+    torch.cuda.synchronize()
+    assert int(z.item()) == 0
+    # exactly the limit passes the limit check (capacity 0 then stops it before any launch)
+    st = lib.csw_sparse_compress_static(t.data_ptr(), C.c_size_t(268435456), out_keep.data_ptr(), 0, z.data_ptr(), None)
+    assert st == 2
     # beyond the fixed array: refused, nothing launched
     big = C.c_size_t(268435456 + 1)
     st = lib.csw_sparse_compress_static(t.data_ptr(), big, t.data_ptr(), 0, t.data_ptr(), None)
