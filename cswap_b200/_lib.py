@@ -49,7 +49,9 @@ class MgrStats(C.Structure):
 class CostModelStruct(C.Structure):
     _fields_ = [(n, C.c_double) for n in
                 ("zfp_enc_a", "zfp_enc_b", "zfp_dec_a", "zfp_dec_b", "sparse_enc_a", "sparse_enc_b", "sparse_dec_a",
-                 "sparse_dec_b", "d2h_a", "d2h_bps", "h2d_a", "h2d_bps")] + [("zfp_maxbits", C.c_uint)]
+                 "sparse_dec_b", "d2h_a", "d2h_bps", "h2d_a", "h2d_bps")] + [("zfp_maxbits", C.c_uint)] + \
+               [(n, C.c_double) for n in ("sparse_enc_b75", "sparse_enc_b90", "sparse_dec_b75", "sparse_dec_b90",
+                                          "host_swap_s")]
 
 
 class TensorDescStruct(C.Structure):
@@ -125,6 +127,8 @@ SIGNATURES = {
     "csw_cost_fit": (_I, [_P, C.POINTER(CostModelStruct)]),
     "csw_cost_decide": (_I, [C.POINTER(CostModelStruct), C.POINTER(TensorDescStruct), _SZ, C.c_double, C.POINTER(_I),
                              C.POINTER(C.c_double)]),
+    "csw_cost_simulate": (_I, [C.POINTER(CostModelStruct), C.POINTER(TensorDescStruct), _SZ, C.c_double, C.POINTER(_I),
+                               C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "csw_host_alloc": (_I, [_SZ, C.POINTER(_P)]),
     "csw_host_free": (_I, [_P]),
     # reference-named entry points

@@ -8,6 +8,8 @@
 // at CSWAP+/resnet-cifar10.cpp:407-437).
 #include <cuda_runtime.h>
 
+#include <time.h>
+
 #include <algorithm>
 #include <cmath>
 #include <cstdint>
@@ -19,15 +21,23 @@
 namespace csw {
 namespace {
 
-// deterministic pseudo-random activations: about half zeros, the rest in (-1,1)
-__global__ void fill_kernel(float* p, size_t n) {
+// deterministic pseudo-random activations: `zeros256` / 256 of them zero, the rest in (-1,1)
+__global__ void fill_kernel(float* p, size_t n, uint32_t zeros256) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     uint32_t h = (uint32_t)i * 2654435761u;
     h ^= h >> 15;
     h *= 2246822519u;
     h ^= h >> 13;
-    p[i] = (h & 1u) ? 0.0f : ((float)(h >> 8) * (1.0f / 8388608.0f) - 1.0f);
+    p[i] = (h & 0xffu) < zeros256 ? 0.0f : ((float)(h >> 8) * (1.0f / 8388608.0f) - 1.0f);
   }
+}
+
+// per-byte slope of the sparse codec at a zero fraction: piecewise linear through the fits at 50, 75 and 90 %
+double sparse_slope(double b50, double b75, double b90, double zf) {
+  if (b75 <= 0 || b90 <= 0 || zf <= 0.5) return b50;
+  if (zf <= 0.75) return b50 + (b75 - b50) * (zf - 0.5) / 0.25;
+  if (zf <= 0.9) return b75 + (b90 - b75) * (zf - 0.75) / 0.15;
+  return b90;
 }
 
 struct Fit {
@@ -113,7 +123,7 @@ csw_status csw_cost_fit(csw_mgr* m, csw_cost_model* model) {
   if (e == cudaSuccess) e = cudaEventCreate(&e0);
   if (e == cudaSuccess) e = cudaEventCreate(&e1);
   if (e == cudaSuccess) {
-    fill_kernel<<<1024, 256, 0, s>>>(d_x, nmax);
+    fill_kernel<<<1024, 256, 0, s>>>(d_x, nmax, 128);
     e = cudaGetLastError();
   }
   st = e == cudaSuccess ? CSW_OK : cuda_fail(e);
@@ -148,8 +158,44 @@ csw_status csw_cost_fit(csw_mgr* m, csw_cost_model* model) {
       }, &t);
     t_h2d.push_back(t);
   }
+  // the sparse codec again at 75 % and 90 % zeros (two largest sizes: the slope is what changes)
+  double slopes[2][2] = {{0, 0}, {0, 0}};
+  const uint32_t zeros256[2] = {192, 230};
+  for (int z = 0; z < 2 && st == CSW_OK; z++) {
+    fill_kernel<<<1024, 256, 0, s>>>(d_x, nmax, zeros256[z]);
+    double te[2] = {0, 0}, td[2] = {0, 0};
+    for (int i = 2; i < 4 && st == CSW_OK; i++) {
+      const size_t n = sizes[i];
+      st = time_op(s, e0, e1, 5, [&] { return csw_sparse_compress_onepass(d_x, n, d_c, L.bound, d_nnz, s); }, &te[i - 2]);
+      if (st == CSW_OK) st = time_op(s, e0, e1, 5, [&] { return csw_sparse_decompress(d_c, n, d_y, s); }, &td[i - 2]);
+    }
+    const double db = (double)(sizes[3] - sizes[2]) * 4;
+    slopes[z][0] = (te[1] - te[0]) / db;
+    slopes[z][1] = (td[1] - td[0]) / db;
+  }
+  // what a swapped tensor costs the calling thread: swap-out + release of a 1 MiB tensor, raw
+  double host_swap = 0;
+  if (st == CSW_OK) {
+    const int reps = 16;
+    csw_ticket* tk[reps];
+    cudaStreamSynchronize(s);
+    timespec t0, t1;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    int made = 0;
+    for (; made < reps; made++)
+      if (csw_swap_out(m, d_x, (size_t)1 << 18, CSW_POLICY_RAW, s, &tk[made]) != CSW_OK) break;
+    for (int i = 0; i < made; i++) csw_ticket_release(m, tk[i]);
+    clock_gettime(CLOCK_MONOTONIC, &t1);
+    if (made) host_swap = ((t1.tv_sec - t0.tv_sec) + (t1.tv_nsec - t0.tv_nsec) * 1e-9) / made;
+    csw_mgr_sync(m);
+  }
   if (st == CSW_OK) {
     Fit f;
+    model->sparse_enc_b75 = slopes[0][0] > 0 ? slopes[0][0] : 0;
+    model->sparse_dec_b75 = slopes[0][1] > 0 ? slopes[0][1] : 0;
+    model->sparse_enc_b90 = slopes[1][0] > 0 ? slopes[1][0] : 0;
+    model->sparse_dec_b90 = slopes[1][1] > 0 ? slopes[1][1] : 0;
+    model->host_swap_s = host_swap;
     f = fit_line(xb, t_ze); model->zfp_enc_a = f.a; model->zfp_enc_b = f.b;
     f = fit_line(xb, t_zd); model->zfp_dec_a = f.a; model->zfp_dec_b = f.b;
     f = fit_line(xb, t_se); model->sparse_enc_a = f.a; model->sparse_enc_b = f.b;
@@ -231,7 +277,9 @@ csw_status csw_cost_decide(const csw_cost_model* cm, const csw_tensor_desc* td, 
   for (size_t i = 0; i < n; i++) {
     const double b = (double)td[i].numel * 4.0, zf = td[i].zero_fraction;
     raw[i] = {CSW_POLICY_RAW, 0, 0, b, true};
-    sparse[i] = {CSW_POLICY_SPARSE, cm->sparse_enc_a + cm->sparse_enc_b * b, cm->sparse_dec_a + cm->sparse_dec_b * b,
+    sparse[i] = {CSW_POLICY_SPARSE,
+                 cm->sparse_enc_a + sparse_slope(cm->sparse_enc_b, cm->sparse_enc_b75, cm->sparse_enc_b90, zf) * b,
+                 cm->sparse_dec_a + sparse_slope(cm->sparse_dec_b, cm->sparse_dec_b75, cm->sparse_dec_b90, zf) * b,
                  b * (1.0 - (zf < 0 ? 0 : zf)) + b / 32.0 + (double)td[i].numel / 1024.0, zf >= 0};
     zfp[i] = {CSW_POLICY_ZFP, cm->zfp_enc_a + cm->zfp_enc_b * b, cm->zfp_dec_a + cm->zfp_dec_b * b, b * rate / 32.0,
               td[i].lossy_ok && td[i].numel >= 1024};
@@ -270,6 +318,35 @@ csw_status csw_cost_decide(const csw_cost_model* cm, const csw_tensor_desc* td, 
     policy[i] = cur[i].policy;
     if (exposed) exposed[i] = stalls[i];
   }
+  return CSW_OK;
+}
+
+csw_status csw_cost_simulate(const csw_cost_model* cm, const csw_tensor_desc* td, size_t n, double fwd_total_s,
+                             const int* policy, double* exposed, double* total_stall_s) {
+  if (!cm || (!td && n) || (!policy && n) || !total_stall_s) return CSW_ERR_ARG;
+  if (cm->d2h_bps <= 0 || cm->h2d_bps <= 0) return CSW_ERR_ARG;
+  const double rate = cm->zfp_maxbits ? cm->zfp_maxbits / 64.0 : 8.0;
+  std::vector<Cand> cur(n);
+  for (size_t i = 0; i < n; i++) {
+    const double b = (double)td[i].numel * 4.0, zf = td[i].zero_fraction;
+    int p = policy[i];
+    if (p == CSW_POLICY_ZFP && td[i].numel < 1024) p = CSW_POLICY_RAW;
+    if (p == CSW_POLICY_SPARSE && zf < 0) p = CSW_POLICY_RAW;
+    if (p == CSW_POLICY_ZFP)
+      cur[i] = {p, cm->zfp_enc_a + cm->zfp_enc_b * b, cm->zfp_dec_a + cm->zfp_dec_b * b, b * rate / 32.0, true};
+    else if (p == CSW_POLICY_SPARSE)
+      cur[i] = {p, cm->sparse_enc_a + sparse_slope(cm->sparse_enc_b, cm->sparse_enc_b75, cm->sparse_enc_b90, zf) * b,
+                cm->sparse_dec_a + sparse_slope(cm->sparse_dec_b, cm->sparse_dec_b75, cm->sparse_dec_b90, zf) * b,
+                b * (1.0 - zf) + b / 32.0 + (double)td[i].numel / 1024.0, true};
+    else if (p == CSW_POLICY_RAW)
+      cur[i] = {p, 0, 0, b, true};
+    else
+      cur[i] = {CSW_POLICY_KEEP, 0, 0, 0, true};
+  }
+  std::vector<double> stalls(n ? n : 1);
+  *total_stall_s = simulate(cm, td, n, cur, fwd_total_s, stalls.data());
+  if (exposed)
+    for (size_t i = 0; i < n; i++) exposed[i] = stalls[i];
   return CSW_OK;
 }
 

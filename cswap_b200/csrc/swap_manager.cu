@@ -139,6 +139,9 @@ struct csw_mgr {
   int device = 0;
   unsigned maxbits = 512;
   cudaStream_t s_codec = nullptr, s_d2h = nullptr, s_h2d = nullptr;
+  // copy out of compressed payloads: a stream of its own, so that a small payload does not
+  // queue behind the large raw copies already waiting for the link (both share it once running)
+  cudaStream_t s_d2h_c = nullptr;
   char* pinned_base = nullptr;
   char* staging_base = nullptr;
   Pool pinned, staging;
@@ -226,13 +229,15 @@ void poll(csw_mgr* m) {
   }
   m->zombies.resize(z);
   size_t k = 0;
-  // `live` is in submission order and every copy out goes down the one D2H
-  // stream, so behind the first unfinished one none has finished either
-  bool d2h_busy = false;
+  // `live` is in submission order; raw copies go down one stream and compressed
+  // payloads down another, so within a kind none has finished behind the first
+  // unfinished one
+  bool busy[2] = {false, false};
   for (size_t i = 0; i < m->live.size(); i++) {
     csw_ticket* t = m->live[i];
     bool keep = true;
     if (t->state == T_OUT) {
+      bool& d2h_busy = busy[t->policy == CSW_POLICY_RAW ? 0 : 1];
       if (!d2h_busy && cudaEventQuery(t->ev_d2h) == cudaSuccess) {
         if (t->policy == CSW_POLICY_SPARSE) finalize_moved(m, t);
         free_stage(m, t);
@@ -306,6 +311,7 @@ csw_status csw_mgr_create(const csw_mgr_config* cfg, csw_mgr** out) {
   cudaDeviceGetStreamPriorityRange(&lo, &hi);
   if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&m->s_codec, cudaStreamNonBlocking, hi);
   if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&m->s_d2h, cudaStreamNonBlocking, hi);
+  if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&m->s_d2h_c, cudaStreamNonBlocking, hi);
   if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&m->s_h2d, cudaStreamNonBlocking, hi);
   if (e == cudaSuccess) e = cudaHostAlloc((void**)&m->pinned_base, pinned, cudaHostAllocPortable | cudaHostAllocMapped);
   if (e == cudaSuccess) e = cudaMalloc((void**)&m->staging_base, staging);
@@ -329,12 +335,14 @@ csw_status csw_mgr_destroy(csw_mgr* m) {
   DeviceGuard g(m->device);
   if (m->s_codec) cudaStreamSynchronize(m->s_codec);
   if (m->s_d2h) cudaStreamSynchronize(m->s_d2h);
+  if (m->s_d2h_c) cudaStreamSynchronize(m->s_d2h_c);
   if (m->s_h2d) cudaStreamSynchronize(m->s_h2d);
   for (csw_ticket* t : m->zombies) destroy_ticket(m, t);
   m->zombies.clear();
   for (cudaEvent_t ev : m->free_events) cudaEventDestroy(ev);
   if (m->s_codec) cudaStreamDestroy(m->s_codec);
   if (m->s_d2h) cudaStreamDestroy(m->s_d2h);
+  if (m->s_d2h_c) cudaStreamDestroy(m->s_d2h_c);
   if (m->s_h2d) cudaStreamDestroy(m->s_h2d);
   if (m->pinned_base) cudaFreeHost(m->pinned_base);
   if (m->staging_base) cudaFree(m->staging_base);
@@ -391,6 +399,7 @@ csw_status csw_swap_out(csw_mgr* m, const float* d_ptr, size_t numel, int policy
     // before the memory it touches goes back to the pools
     cudaStreamSynchronize(m->s_codec);
     cudaStreamSynchronize(m->s_d2h);
+    cudaStreamSynchronize(m->s_d2h_c);
     cudaGetLastError();
     if (t->host) m->pinned.release(t->host, t->host_cap);
     free_stage(m, t);
@@ -434,9 +443,9 @@ csw_status csw_swap_out(csw_mgr* m, const float* d_ptr, size_t numel, int policy
                           cudaMemcpyDeviceToDevice, m->s_codec);
     if (st == CSW_OK && e == cudaSuccess) {
       e = cudaEventRecord(t->ev_read, m->s_codec);
-      if (e == cudaSuccess) e = cudaStreamWaitEvent(m->s_d2h, t->ev_read, 0);
-      if (e == cudaSuccess) e = cudaMemcpyAsync(t->host, t->stage, zbytes, cudaMemcpyDeviceToHost, m->s_d2h);
-      if (e == cudaSuccess) e = cudaEventRecord(t->ev_d2h, m->s_d2h);
+      if (e == cudaSuccess) e = cudaStreamWaitEvent(m->s_d2h_c, t->ev_read, 0);
+      if (e == cudaSuccess) e = cudaMemcpyAsync(t->host, t->stage, zbytes, cudaMemcpyDeviceToHost, m->s_d2h_c);
+      if (e == cudaSuccess) e = cudaEventRecord(t->ev_d2h, m->s_d2h_c);
     }
     t->moved = zbytes;
     t->moved_final = true;
@@ -448,14 +457,14 @@ csw_status csw_swap_out(csw_mgr* m, const float* d_ptr, size_t numel, int policy
     st = csw_sparse_compress_onepass(d_ptr, numel, t->stage, t->stage_cap, nnz_dev, m->s_codec);
     if (st == CSW_OK) {
       e = cudaEventRecord(t->ev_read, m->s_codec);
-      if (e == cudaSuccess) e = cudaStreamWaitEvent(m->s_d2h, t->ev_read, 0);
+      if (e == cudaSuccess) e = cudaStreamWaitEvent(m->s_d2h_c, t->ev_read, 0);
       if (e == cudaSuccess) {
-        sparse_to_host_kernel<<<32, 256, 0, m->s_d2h>>>(reinterpret_cast<const uint4*>(t->stage),
+        sparse_to_host_kernel<<<32, 256, 0, m->s_d2h_c>>>(reinterpret_cast<const uint4*>(t->stage),
                                                         reinterpret_cast<uint4*>(t->host), nnz_dev, t->nnz_host,
                                                         L.values);
         e = cudaGetLastError();
       }
-      if (e == cudaSuccess) e = cudaEventRecord(t->ev_d2h, m->s_d2h);
+      if (e == cudaSuccess) e = cudaEventRecord(t->ev_d2h, m->s_d2h_c);
     }
     t->moved = L.bound;  // upper bound until the count lands
   }
@@ -520,7 +529,7 @@ static csw_status load_stage(csw_mgr* m, csw_ticket* t) {
         e = get_event(m, &t->ev_h2d);
         if (e != cudaSuccess) return cuda_fail(e);
       }
-      e = cudaEventRecord(t->ev_h2d, m->s_d2h);
+      e = cudaEventRecord(t->ev_h2d, m->s_d2h_c);
       return e == cudaSuccess ? CSW_OK : cuda_fail(e);
     }
   }
@@ -779,6 +788,7 @@ csw_status csw_mgr_sync(csw_mgr* m) {
   DeviceGuard g(m->device);
   cudaError_t e = cudaStreamSynchronize(m->s_codec);
   if (e == cudaSuccess) e = cudaStreamSynchronize(m->s_d2h);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(m->s_d2h_c);
   if (e == cudaSuccess) e = cudaStreamSynchronize(m->s_h2d);
   if (e != cudaSuccess) return cuda_fail(e);
   poll(m);

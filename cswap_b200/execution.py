@@ -297,8 +297,17 @@ class Execution:
                 "start": self._prof_start, "end": ev, "numel": y.numel(), "zero_fraction": zf,
                 "inputs": [getattr(t, "tensor_id", -1) for t in inputs], "omit": isomit,
                 "type": int(layer_type), "float32": y.dtype == torch.float32, "has_grad": y.grad_fn is not None,
-                "recomputable": forward is not None,
+                "recomputable": forward is not None, "bwd": None,
             }
+            if y.grad_fn is not None:
+                # when this layer's backward begins: what a tensor it consumed has to be back by
+                def mark(_grads, idx=self.index):
+                    rec = self._prof.get(idx)
+                    if rec is not None and rec["bwd"] is None:
+                        e = torch.cuda.Event(enable_timing=True)
+                        e.record()
+                        rec["bwd"] = e
+                y.grad_fn.register_prehook(mark)
             # which consumed tensors autograd holds on to once this consumer has run
             for t in inputs:
                 tid = getattr(t, "tensor_id", -1)
@@ -321,8 +330,12 @@ class Execution:
         """Turn the events of a profiled iteration into numbers (synchronises)."""
         torch.cuda.synchronize()
         out = {}
+        marks = [i for i in sorted(self._prof) if self._prof[i].get("bwd") is not None]
+        first = self._prof[marks[-1]]["bwd"] if marks else None  # backward starts at the last layer
         for idx, p in self._prof.items():
             out[idx] = {
+                "bwd_start_s": first.elapsed_time(p["bwd"]) * 1e-3 if first is not None and p.get("bwd") is not None
+                else -1.0,
                 "time_s": p["start"].elapsed_time(p["end"]) * 1e-3, "numel": p["numel"],
                 "zero_fraction": float(p["zero_fraction"]) if p["zero_fraction"] is not None else -1.0,
                 "inputs": p["inputs"], "omit": p["omit"], "type": p["type"], "float32": p["float32"],
@@ -363,8 +376,11 @@ class Execution:
                 continue  # nothing keeps it for backward: it dies after its consumer and costs no link time
             c = consumer[tid]
             cands.append(tid)
-            descs.append(TensorDesc(p["numel"], p["zero_fraction"], tid in lossy, ready_s=start[c],
-                                    need_s=bwd_factor * (fwd_total - start[c + 1])))
+            # needed when the consumer's backward begins: measured where the profiled iteration
+            # ran backward, else estimated from the forward times of the later layers
+            measured = prof.get(c, {}).get("bwd_start_s", -1.0)
+            need = measured if measured >= 0 else bwd_factor * (fwd_total - start[c + 1])
+            descs.append(TensorDesc(p["numel"], p["zero_fraction"], tid in lossy, ready_s=start[c], need_s=need))
         return n, fwd_total, consumer, cands, descs
 
     def make_policy(self, prof: Dict[int, dict], cost: CostModel, lossy_ids: Optional[Sequence[int]] = None,

@@ -288,6 +288,21 @@ class CostModel:
         check(lib().csw_cost_decide(C.byref(self.c), arr, n, fwd_total_s, pol, exp), "csw_cost_decide")
         return list(pol[:n]), list(exp[:n])
 
+    def simulate(self, tensors: Sequence[TensorDesc], policy: Sequence[int], fwd_total_s: float = 0.0
+                 ) -> Tuple[float, List[float]]:
+        """Modelled stall (seconds) of a step that swaps `tensors` under the
+        given policy codes: (total, per tensor)."""
+        n = len(tensors)
+        arr = (TensorDescStruct * max(n, 1))()
+        for i, t in enumerate(tensors):
+            arr[i] = TensorDescStruct(t.numel, t.zero_fraction, int(t.lossy_ok), t.ready_s, t.need_s)
+        pol = (C.c_int * max(n, 1))(*policy)
+        exp = (C.c_double * max(n, 1))()
+        total = C.c_double()
+        check(lib().csw_cost_simulate(C.byref(self.c), arr, n, fwd_total_s, pol, exp, C.byref(total)),
+              "csw_cost_simulate")
+        return total.value, list(exp[:n])
+
     def as_dict(self) -> dict:
         return {k: getattr(self.c, k) for k in _COST_FIELDS}
 

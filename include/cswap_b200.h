@@ -282,9 +282,16 @@ csw_status csw_mgr_sync(csw_mgr* m);
  * for each codec direction, and link bandwidths in bytes/second. */
 typedef struct {
   double zfp_enc_a, zfp_enc_b, zfp_dec_a, zfp_dec_b;         /* at the manager's maxbits */
-  double sparse_enc_a, sparse_enc_b, sparse_dec_a, sparse_dec_b;
+  double sparse_enc_a, sparse_enc_b, sparse_dec_a, sparse_dec_b; /* at 50 % zeros        */
   double d2h_a, d2h_bps, h2d_a, h2d_bps;                     /* latency + bandwidth      */
   unsigned zfp_maxbits;
+  /* per-byte slopes of the sparse codec at 75 % and 90 % zeros (the intercepts
+   * are shared with the 50 % fit); 0 means "not fitted": the 50 % slope is used.
+   * The decision interpolates between the three by the tensor's zero fraction. */
+  double sparse_enc_b75, sparse_enc_b90, sparse_dec_b75, sparse_dec_b90;
+  /* host time of one csw_swap_out + csw_ticket_release pair, seconds (what a
+   * swapped tensor costs the thread that drives the model, whatever the policy) */
+  double host_swap_s;
 } csw_cost_model;
 
 /* Measure the codecs and the host link on the manager's device (a few
@@ -313,6 +320,12 @@ typedef struct {
  * and, if non-NULL, each tensor's modelled stall in seconds to `exposed`. */
 csw_status csw_cost_decide(const csw_cost_model* model, const csw_tensor_desc* tensors, size_t n, double fwd_total_s,
                            int* policy, double* exposed);
+/* The same simulation for a policy vector the caller supplies (KEEP, RAW,
+ * SPARSE or ZFP per tensor): each tensor's modelled stall to `exposed` (may be
+ * NULL) and their sum to *total_stall_s.  A choice the tensor does not allow
+ * (ZFP on fewer than 1024 values, SPARSE without a zero fraction) counts as RAW. */
+csw_status csw_cost_simulate(const csw_cost_model* model, const csw_tensor_desc* tensors, size_t n, double fwd_total_s,
+                             const int* policy, double* exposed, double* total_stall_s);
 
 /* ---- pinned host memory helpers (for callers without a CUDA binding) ------ */
 csw_status csw_host_alloc(size_t bytes, void** p);

@@ -69,6 +69,7 @@ struct LayerProfile {
   bool omit = false;
   int type = ACT;
   bool float32 = false, has_grad = false, saved = true, recomputable = false;
+  double bwd_start_s = -1;  // backward compute that ran before this layer's own backward began (-1: not seen)
 };
 
 class Execution {
@@ -154,10 +155,15 @@ class Execution {
   std::map<int, LayerProfile> finish_profile() {
     c10::cuda::device_synchronize();
     std::map<int, LayerProfile> out;
+    // backward runs the layers last to first: the mark of the last layer seen is where it began
+    const ProfEntry* first = nullptr;
+    for (auto it = prof_.rbegin(); it != prof_.rend() && !first; ++it)
+      if (it->second.bwd_seen) first = &it->second;
     for (auto& kv : prof_) {
       LayerProfile p = kv.second.p;
       p.time_s = kv.second.start.elapsed_time(kv.second.end) * 1e-3;
       if (kv.second.zeros.defined()) p.zero_fraction = kv.second.zeros.item<double>();
+      if (first && kv.second.bwd_seen) p.bwd_start_s = first->bwd.elapsed_time(kv.second.bwd) * 1e-3;
       out[kv.first] = p;
     }
     prof_.clear();
@@ -189,58 +195,44 @@ class Execution {
   std::vector<int> make_policy(const std::map<int, LayerProfile>& prof, const std::set<int>* lossy_ids = nullptr,
                                double bwd_factor = 2.0, size_t min_bytes = size_t(1) << 20,
                                bool all_zfp_where_allowed = false) {
-    const int n = prof.empty() ? 0 : prof.rbegin()->first + 1;
-    std::vector<double> start(n + 1, 0.0);
-    for (int i = 0; i < n; i++) {
-      auto it = prof.find(i);
-      start[i + 1] = start[i] + (it == prof.end() ? 0.0 : it->second.time_s);
+    Candidates c = candidates(prof, lossy_ids, bwd_factor, min_bytes);
+    if ((int)policy.size() < c.n) {
+      policy.resize(c.n, 0);
+      begin_stage.resize(c.n, 0);
     }
-    const double fwd_total = start[n];
-    std::map<int, int> consumer;
-    std::set<int> conv_inputs;
-    for (auto& kv : prof)
-      for (int tid : kv.second.inputs)
-        if (tid >= 0 && !consumer.count(tid)) {
-          consumer[tid] = kv.first;
-          if (kv.second.type == CONV) conv_inputs.insert(tid);
-        }
-    const std::set<int>& lossy = lossy_ids ? *lossy_ids : conv_inputs;
-    if ((int)policy.size() < n) {
-      policy.resize(n, 0);
-      begin_stage.resize(n, 0);
-    }
-    std::vector<std::pair<int, int>> by_consumer;  // (consumer, id)
-    for (auto& kv : consumer) by_consumer.push_back({kv.second, kv.first});
-    std::sort(by_consumer.begin(), by_consumer.end());
-    std::vector<int> cands;
-    std::vector<csw_tensor_desc> descs;
-    for (auto& ci : by_consumer) {
-      auto it = prof.find(ci.second);
-      if (it == prof.end()) continue;
-      const LayerProfile& p = it->second;
-      if (p.omit || !p.float32 || !p.has_grad || p.numel * 4 < min_bytes || !p.saved) continue;
-      csw_tensor_desc d{};
-      d.numel = p.numel;
-      d.zero_fraction = p.zero_fraction;
-      d.lossy_ok = lossy.count(ci.second) ? 1 : 0;
-      d.ready_s = start[ci.first];
-      d.need_s = bwd_factor * (fwd_total - start[ci.first + 1]);
-      cands.push_back(ci.second);
-      descs.push_back(d);
-    }
-    std::vector<int> pol(descs.size() ? descs.size() : 1);
+    std::vector<int> pol(c.descs.size() ? c.descs.size() : 1);
     std::vector<double> stall(pol.size());
-    if (!descs.empty())
-      check(csw_cost_decide(&cost_model(), descs.data(), descs.size(), fwd_total, pol.data(), stall.data()),
+    if (!c.descs.empty())
+      check(csw_cost_decide(&cost_model(), c.descs.data(), c.descs.size(), c.fwd_total, pol.data(), stall.data()),
             "csw_cost_decide");
-    for (int i = 0; i < n; i++) policy[i] = 0;
-    for (size_t k = 0; k < cands.size(); k++) {
+    for (int i = 0; i < c.n; i++) policy[i] = 0;
+    for (size_t k = 0; k < c.ids.size(); k++) {
       int p = pol[k];
-      if (all_zfp_where_allowed && descs[k].lossy_ok && descs[k].numel >= 1024) p = CSW_POLICY_ZFP;
-      policy[cands[k]] = p;
-      begin_stage[cands[k]] = consumer[cands[k]];
+      if (all_zfp_where_allowed && c.descs[k].lossy_ok && c.descs[k].numel >= 1024) p = CSW_POLICY_ZFP;
+      policy[c.ids[k]] = p;
+      begin_stage[c.ids[k]] = c.consumer[c.ids[k]];
     }
     return policy;
+  }
+
+  // What the cost model expects the current policy table to cost: the step's
+  // modelled stall in seconds (link and codec time that compute does not hide)
+  // plus the host time of the swaps themselves.
+  double predicted_overhead_s(const std::map<int, LayerProfile>& prof, double bwd_factor = 2.0) {
+    Candidates c = candidates(prof, nullptr, bwd_factor, 0);
+    std::vector<int> pol;
+    size_t swaps = 0;
+    for (int id : c.ids) {
+      int p = id < (int)policy.size() ? policy[id] : 0;
+      if (p != CSW_POLICY_RAW && p != CSW_POLICY_SPARSE && p != CSW_POLICY_ZFP) p = CSW_POLICY_KEEP;
+      swaps += p != CSW_POLICY_KEEP;
+      pol.push_back(p);
+    }
+    double total = 0;
+    if (!c.descs.empty())
+      check(csw_cost_simulate(&cost_model(), c.descs.data(), c.descs.size(), c.fwd_total, pol.data(), nullptr, &total),
+            "csw_cost_simulate");
+    return total + swaps * cost_model().host_swap_s;
   }
 
   csw_mgr* manager() const { return mgr_; }
@@ -302,11 +294,78 @@ class Execution {
     }
   };
 
+  // Profiling: marks the moment a layer's backward begins.
+  struct BackwardMark : torch::autograd::FunctionPreHook {
+    Execution* exe;
+    int layer;
+    BackwardMark(Execution* e, int l) : exe(e), layer(l) {}
+    torch::autograd::variable_list operator()(const torch::autograd::variable_list& grads) override {
+      auto it = exe->prof_.find(layer);
+      if (exe->profile && it != exe->prof_.end() && !it->second.bwd_seen) {
+        it->second.bwd.record(c10::cuda::getCurrentCUDAStream());
+        it->second.bwd_seen = true;
+      }
+      return grads;
+    }
+  };
+
   struct ProfEntry {
-    at::cuda::CUDAEvent start{cudaEventDefault}, end{cudaEventDefault};
+    at::cuda::CUDAEvent start{cudaEventDefault}, end{cudaEventDefault}, bwd{cudaEventDefault};
+    bool bwd_seen = false;
     torch::Tensor zeros;  // fraction of zeros in the output, still on the device
     LayerProfile p;
   };
+
+  // Swap candidates of a profiled iteration, in the order their consumers run,
+  // with what the cost model needs to know about each.
+  struct Candidates {
+    int n = 0;
+    double fwd_total = 0;
+    std::map<int, int> consumer;
+    std::vector<int> ids;
+    std::vector<csw_tensor_desc> descs;
+  };
+  static Candidates candidates(const std::map<int, LayerProfile>& prof, const std::set<int>* lossy_ids,
+                               double bwd_factor, size_t min_bytes) {
+    Candidates c;
+    c.n = prof.empty() ? 0 : prof.rbegin()->first + 1;
+    std::vector<double> start(c.n + 1, 0.0);
+    for (int i = 0; i < c.n; i++) {
+      auto it = prof.find(i);
+      start[i + 1] = start[i] + (it == prof.end() ? 0.0 : it->second.time_s);
+    }
+    c.fwd_total = start[c.n];
+    std::set<int> conv_inputs;
+    for (auto& kv : prof)
+      for (int tid : kv.second.inputs)
+        if (tid >= 0 && !c.consumer.count(tid)) {
+          c.consumer[tid] = kv.first;
+          if (kv.second.type == CONV) conv_inputs.insert(tid);
+        }
+    const std::set<int>& lossy = lossy_ids ? *lossy_ids : conv_inputs;
+    std::vector<std::pair<int, int>> by_consumer;  // (consumer, id)
+    for (auto& kv : c.consumer) by_consumer.push_back({kv.second, kv.first});
+    std::sort(by_consumer.begin(), by_consumer.end());
+    for (auto& ci : by_consumer) {
+      auto it = prof.find(ci.second);
+      if (it == prof.end()) continue;
+      const LayerProfile& p = it->second;
+      if (p.omit || !p.float32 || !p.has_grad || p.numel * 4 < min_bytes || !p.saved) continue;
+      csw_tensor_desc d{};
+      d.numel = p.numel;
+      d.zero_fraction = p.zero_fraction;
+      d.lossy_ok = lossy.count(ci.second) ? 1 : 0;
+      d.ready_s = start[ci.first];
+      // the tensor is needed when its consumer's backward begins: measured in the profiled
+      // iteration where that was seen, else estimated from the forward times of the later layers
+      auto cit = prof.find(ci.first);
+      d.need_s = cit != prof.end() && cit->second.bwd_start_s >= 0 ? cit->second.bwd_start_s
+                                                                  : bwd_factor * (c.fwd_total - start[ci.first + 1]);
+      c.ids.push_back(ci.second);
+      c.descs.push_back(d);
+    }
+    return c;
+  }
 
   static void check(csw_status st, const char* what) {
     if (st != CSW_OK) throw std::runtime_error(std::string(what) + ": " + csw_status_string(st));
@@ -433,6 +492,7 @@ class Execution {
       e.p.float32 = x.scalar_type() == torch::kFloat32;
       e.p.has_grad = (bool)fn;
       e.p.recomputable = (bool)producer && n_in == 1;
+      if (fn) fn->add_pre_hook(std::make_unique<BackwardMark>(this, index));
       if (x.is_cuda() && e.p.float32) e.zeros = (x.detach() == 0).to(torch::kFloat64).mean();
       for (size_t i = 0; i < n_in; i++) {
         const int tid = id_of(*inputs[i]);

@@ -469,7 +469,32 @@ static int run_bench(int batch, int steps, int warmup, int seed) {
     o << ", \"self_tuned_chosen\": \"" << chosen << "\", \"self_tuned_policy_counts\": {\"0\": " << counts[0]
       << ", \"2\": " << counts[2] << ", \"3\": " << counts[3] << ", \"6\": " << counts[6] << "}";
     const csw_cost_model& cm = exe.cost_model();
-    o << ", \"cost_model\": {\"d2h_GBps\": " << cm.d2h_bps / 1e9 << ", \"h2d_GBps\": " << cm.h2d_bps / 1e9 << "}";
+    o << ", \"cost_model\": {\"d2h_GBps\": " << cm.d2h_bps / 1e9 << ", \"h2d_GBps\": " << cm.h2d_bps / 1e9
+      << ", \"host_swap_us\": " << cm.host_swap_s * 1e6 << ", \"sparse_enc_ps_per_byte\": [" << cm.sparse_enc_b * 1e12
+      << ", " << cm.sparse_enc_b75 * 1e12 << ", " << cm.sparse_enc_b90 * 1e12 << "]}";
+    // what the model expects each table to add to the no-swap step, beside what it measured
+    o << ", \"predicted_vs_measured_overhead_ms\": {";
+    const std::vector<int> tuned = exe.policy, tuned_begin = exe.begin_stage;
+    struct Case { const char* name; int fill; };
+    bool first = true;
+    for (Case c : {Case{"raw_swap", CSW_POLICY_RAW}, Case{"zfp8_everywhere", CSW_POLICY_ZFP}, Case{"self_tuned", -1}}) {
+      if (c.fill >= 0) {
+        for (int i = 0; i < 50; i++) {
+          exe.begin_stage[i] = i + 1;
+          exe.policy[i] = c.fill;
+        }
+      } else {
+        exe.policy = tuned;
+        exe.begin_stage = tuned_begin;
+      }
+      const double predicted = exe.predicted_overhead_s(prof) * 1e3;
+      const double measured = timed_steps(net, exe, b, steps, warmup).ms_median - none.ms_median;
+      o << (first ? "" : ", ") << "\"" << c.name << "\": [" << predicted << ", " << measured << "]";
+      first = false;
+    }
+    o << "}";
+    exe.policy = tuned;
+    exe.begin_stage = tuned_begin;
   }
   const std::vector<double> eps = {0.1, 0.25, 0.5, 1.0};
   const double t0 = none.ms_median;

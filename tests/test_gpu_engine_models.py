@@ -47,9 +47,12 @@ class _NullExecution:
 class _CodecOnSaved(_NullExecution):
     """Engine-free stand-in for policy 6.  A tensor with a chosen id that the
     layer right after its producer consumes (the engine's begin_stage = id + 1
-    rule) is marked; every tensor autograd saved on a marked storage is replaced
-    by decode(encode(x)) when backward asks for it.  Values past the last whole
-    32 x 32 slab travel as they are, as in the swap manager."""
+    rule) is marked; every tensor autograd saved on a marked storage up to and
+    including that layer is replaced by decode(encode(x)) when backward asks for
+    it (a later layer that reads the same tensor again in forward still sees, and
+    saves, the exact values: the engine only lets go of the device copy that its
+    own records hold).  Values past the last whole 32 x 32 slab travel as they
+    are, as in the swap manager."""
 
     def __init__(self, cs, lossy_ids, maxbits):
         super().__init__()
@@ -75,7 +78,7 @@ class _CodecOnSaved(_NullExecution):
             if not (t.is_cuda and t.dtype == torch.float32 and t.is_contiguous() and t.storage_offset() == 0
                     and t.numel() >= 1024 and t.untyped_storage().nbytes() == 4 * t.numel()):
                 continue
-            self.lossy_ptrs[t.untyped_storage().data_ptr()] = t.numel()
+            self.lossy_ptrs[t.untyped_storage().data_ptr()] = (t.numel(), self.index)
 
     def postforward(self):
         self.hooks.__exit__(None, None, None)
@@ -84,7 +87,8 @@ class _CodecOnSaved(_NullExecution):
         for h in self.handles:
             t = h[0]
             ptr = t.untyped_storage().data_ptr()
-            if ptr in self.lossy_ptrs and t.numel() == self.lossy_ptrs[ptr] and t.is_contiguous():
+            if ptr in self.lossy_ptrs and t.numel() == self.lossy_ptrs[ptr][0] and t.is_contiguous() \
+                    and t.storage_offset() == 0 and h[1] <= self.lossy_ptrs[ptr][1]:
                 if ptr not in done:
                     flat = t.detach().reshape(-1).clone()
                     whole = flat.numel() // 1024 * 1024
@@ -95,7 +99,7 @@ class _CodecOnSaved(_NullExecution):
                 h[0] = done[ptr].view(t.shape)
 
     def _pack(self, t):
-        h = [t]
+        h = [t, self.index]
         self.handles.append(h)
         return h
 
