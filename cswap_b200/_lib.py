@@ -116,6 +116,8 @@ SIGNATURES = {
     "csw_swap_out_wait": (_I, [_P, _P, _P]),
     "csw_prefetch": (_I, [_P, _P]),
     "csw_swap_in": (_I, [_P, _P, _P, _P]),
+    "csw_swap_in_start": (_I, [_P, _P, _P, _P]),
+    "csw_swap_in_wait": (_I, [_P, _P, _P]),
     "csw_ticket_release": (_I, [_P, _P]),
     "csw_ticket_query": (_I, [_P, _P, C.POINTER(TicketInfo)]),
     "csw_ticket_export": (_I, [_P, _P, _P, _SZ, C.POINTER(_SZ)]),

@@ -564,6 +564,20 @@ csw_status csw_prefetch(csw_mgr* m, csw_ticket* t) {
 }
 
 csw_status csw_swap_in(csw_mgr* m, csw_ticket* t, float* d_dst, csw_stream_t compute) {
+  csw_status st = csw_swap_in_start(m, t, d_dst, compute);
+  return st == CSW_OK ? csw_swap_in_wait(m, t, compute) : st;
+}
+
+csw_status csw_swap_in_wait(csw_mgr* m, csw_ticket* t, csw_stream_t compute) {
+  if (!m || !t) return CSW_ERR_ARG;
+  std::lock_guard<std::mutex> lk(m->mu);
+  DeviceGuard g(m->device);
+  if (t->state == T_DEAD || !t->ev_done) return CSW_ERR_STATE;  // no csw_swap_in_start before it
+  cudaError_t e = cudaStreamWaitEvent(compute, t->ev_done, 0);
+  return e == cudaSuccess ? CSW_OK : cuda_fail(e);
+}
+
+csw_status csw_swap_in_start(csw_mgr* m, csw_ticket* t, float* d_dst, csw_stream_t compute) {
   if (!m || !t || !d_dst) return CSW_ERR_ARG;
   std::lock_guard<std::mutex> lk(m->mu);
   DeviceGuard g(m->device);
@@ -608,7 +622,6 @@ csw_status csw_swap_in(csw_mgr* m, csw_ticket* t, float* d_dst, csw_stream_t com
     if (st != CSW_OK) return st;
     e = cudaEventRecord(t->ev_done, m->s_codec);
   }
-  if (e == cudaSuccess) e = cudaStreamWaitEvent(compute, t->ev_done, 0);
   if (e != cudaSuccess) return cuda_fail(e);
   t->state = T_IN;
   if (!t->in_live) {

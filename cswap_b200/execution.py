@@ -59,7 +59,8 @@ class _Record:
     """Residency of one activation storage: on the device (`tensor`) or
     swapped out (`ticket`)."""
 
-    __slots__ = ("tensor", "ticket", "numel", "order", "exe", "producer", "dropped", "saved", "__weakref__")
+    __slots__ = ("tensor", "ticket", "numel", "order", "exe", "producer", "dropped", "saved", "ahead",
+                 "__weakref__")
 
     def __init__(self, tensor: torch.Tensor, exe: "Execution"):
         self.tensor: Optional[torch.Tensor] = tensor
@@ -70,11 +71,16 @@ class _Record:
         self.producer = None   # (callable, packed inputs) when the driver passed the layer to post()
         self.dropped = False   # policy 1: let go without a copy, rebuilt by `producer`
         self.saved = False     # autograd holds it for backward (a pack hook has seen it)
+        self.ahead = None      # destination of a swap-in started before the tensor was asked for
 
     def materialize(self) -> torch.Tensor:
         if self.tensor is None:
             exe = self.exe()
-            if self.ticket is not None:
+            if self.ticket is not None and self.ahead is not None:
+                exe.mgr.swap_in_wait(self.ticket)   # copy and decode were started one step earlier
+                self.tensor, self.ahead = self.ahead.view(-1), None
+                exe._after_swap_in(self)
+            elif self.ticket is not None:
                 back = exe.mgr.reclaim(self.ticket)
                 if back is not None:
                     # needed again before it had left the device: take it back as it is
@@ -95,6 +101,12 @@ class _Record:
 
     def __del__(self):
         t = self.ticket
+        if self.ahead is not None and t is not None:
+            # a swap-in started ahead of time that nobody waited for may still be writing its tensor
+            try:
+                self.exe().mgr.sync()
+            except Exception:
+                pass
         if t is not None:
             try:
                 t.release()
@@ -218,8 +230,10 @@ class Execution:
             r = self._swapped[i]() if i < len(self._swapped) else None
             if r is not None and r.tensor is None and r.ticket is not None:
                 # a lossless ticket still on its way out may yet be taken back whole
-                if r.ticket.policy == POLICY_ZFP or self.mgr.out_done(r.ticket):
-                    self.mgr.prefetch(r.ticket)
+                if (r.ticket.policy == POLICY_ZFP or self.mgr.out_done(r.ticket)) and r.ahead is None:
+                    # copy AND decode, into a tensor taken now, so that the consumer's backward
+                    # finds it ready instead of waiting for a decode that starts when it asks
+                    r.ahead = self.mgr.swap_in_start(r.ticket)
                 break
 
     # ---- pre / post ----------------------------------------------------------------

@@ -233,6 +233,23 @@ class SwapManager:
         self._poll()
         return out
 
+    def swap_in_start(self, ticket: Ticket, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """First half of swap_in: copy and decode are enqueued behind the work
+        already on the current stream, which is not made to wait.  Call
+        swap_in_wait before the tensor is used."""
+        if out is None:
+            out = torch.empty(ticket.shape, dtype=torch.float32, device=ticket.device)
+        _require_cuda_f32(out, "out")
+        if out.numel() != ticket.numel:
+            raise ValueError("out has the wrong number of elements")
+        check(lib().csw_swap_in_start(self._h, ticket._h, out.data_ptr(), _stream_ptr(out.device)),
+              "csw_swap_in_start")
+        return out
+
+    def swap_in_wait(self, ticket: Ticket) -> None:
+        check(lib().csw_swap_in_wait(self._h, ticket._h, _stream_ptr(self.device)), "csw_swap_in_wait")
+        self._poll()
+
     def stats(self) -> dict:
         s = MgrStats()
         check(lib().csw_mgr_get_stats(self._h, C.byref(s)), "csw_mgr_get_stats")

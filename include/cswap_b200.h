@@ -221,6 +221,14 @@ csw_status csw_swap_out_wait(csw_mgr* m, csw_ticket* t, csw_stream_t stream);
  * wait for the result.  csw_prefetch starts the host -> device copy early. */
 csw_status csw_prefetch(csw_mgr* m, csw_ticket* t);
 csw_status csw_swap_in(csw_mgr* m, csw_ticket* t, float* d_dst, csw_stream_t compute);
+/* The same in two halves, for bringing a tensor back before it is asked for:
+ * csw_swap_in_start enqueues copy and decode into d_dst behind the work already
+ * on `compute` (d_dst may still be in use by it) but does not make `compute`
+ * wait; csw_swap_in_wait, called when the tensor is needed, makes `compute` wait
+ * for the result.  csw_swap_in is the two back to back.  (No counterpart in the
+ * reference, whose engine brings a tensor back when its consumer runs.) */
+csw_status csw_swap_in_start(csw_mgr* m, csw_ticket* t, float* d_dst, csw_stream_t compute);
+csw_status csw_swap_in_wait(csw_mgr* m, csw_ticket* t, csw_stream_t compute);
 /* Give the ticket up.  Never blocks: its host and staging memory return to the
  * pools at once if no copy is in flight, else when a later call on the manager
  * finds them finished.  The handle is invalid afterwards. */

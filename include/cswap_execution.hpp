@@ -265,10 +265,13 @@ class Execution {
     bool restored = false;
     bool started = false;   // the copy out (or the drop) has been issued
     at::DataPtr reading;    // the device block while the manager still reads it
+    at::DataPtr ahead;      // destination of a swap-in started before the tensor was asked for
     // policy 1: how to rebuild the tensor
     Producer producer;
     torch::Tensor producer_input;
     ~Swapped() {
+      // a swap-in started ahead of time that nobody waited for may still be writing its block
+      if (ahead.get() != nullptr && exe && exe->mgr_) csw_mgr_sync(exe->mgr_);
       if (ticket && exe && exe->mgr_) csw_ticket_release(exe->mgr_, ticket);
     }
   };
@@ -554,19 +557,30 @@ class Execution {
       }
     }
     auto* alloc = c10::cuda::CUDACachingAllocator::get();
-    at::DataPtr dp = alloc->allocate(s.nbytes);
-    check(csw_swap_in(mgr_, s.ticket, static_cast<float*>(dp.get()), c10::cuda::getCurrentCUDAStream().stream()),
-          "csw_swap_in");
-    s.storage->set_data_ptr_noswap(std::move(dp));
+    const cudaStream_t stream = c10::cuda::getCurrentCUDAStream().stream();
+    if (s.ahead.get() != nullptr) {
+      // copy and decode were started when the tensor swapped out after this one came back
+      check(csw_swap_in_wait(mgr_, s.ticket, stream), "csw_swap_in_wait");
+      s.storage->set_data_ptr_noswap(std::move(s.ahead));
+    } else {
+      at::DataPtr dp = alloc->allocate(s.nbytes);
+      check(csw_swap_in(mgr_, s.ticket, static_cast<float*>(dp.get()), stream), "csw_swap_in");
+      s.storage->set_data_ptr_noswap(std::move(dp));
+    }
     s.restored = true;
-    // one step ahead: start bringing back the tensor swapped out just before this one
+    // One step ahead: start bringing back - copy AND decode, into a block taken now - the
+    // tensor swapped out just before this one, so that its consumer's backward finds it
+    // ready instead of waiting for a decode that starts only when it asks.
     for (int i = s.order - 1; i >= 0; i--) {
       auto p = order_[i].lock();
       if (p && !p->restored && p->ticket) {
         int done = 1;
         // a lossless ticket still on its way out may yet be taken back whole
         if (p->policy != CSW_POLICY_ZFP) csw_swap_out_done(mgr_, p->ticket, &done);
-        if (done) csw_prefetch(mgr_, p->ticket);
+        if (done && p->ahead.get() == nullptr) {
+          p->ahead = alloc->allocate(p->nbytes);
+          check(csw_swap_in_start(mgr_, p->ticket, static_cast<float*>(p->ahead.get()), stream), "csw_swap_in_start");
+        }
         break;
       }
     }
