@@ -47,6 +47,29 @@ if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
     os.environ["NCCL_DEBUG"] = "WARN"
 
 
+# Standard output carries exactly one JSON line.  Libraries print there too (NCCL's
+# version banner, the reference's timing lines), so file descriptor 1 is pointed at
+# standard error for the run and the line goes to the descriptor saved here.
+_REAL_STDOUT = None
+
+
+def guard_stdout():
+    global _REAL_STDOUT
+    if _REAL_STDOUT is None:
+        sys.stdout.flush()
+        _REAL_STDOUT = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line) -> None:
+    data = (json.dumps(line) + "\n").encode()
+    sys.stdout.flush()
+    if _REAL_STDOUT is None:
+        os.write(1, data)
+    else:
+        os.write(_REAL_STDOUT, data)
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -275,7 +298,7 @@ def run_reference(args):
                 "algorithm, pinned against a host build of the reference's own headers and against the output "
                 "of its CUDA kernels; reference_cuda times those kernels themselves on this GPU",
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 def max_over_ranks(values, device="cpu"):
@@ -452,7 +475,7 @@ def run_model_workload(args):
         if rank == 0:
             line["cpp_host_side"] = cpp
     if rank == 0:
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
@@ -616,6 +639,7 @@ def vgg16_block(args, cs, torch, dev, world, rank):
 
 def main():
     args = parse()
+    guard_stdout()
     if args.impl == "reference":
         run_reference(args)
         return
@@ -795,7 +819,7 @@ def main():
             "config": workload_config(args), "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": 2 * args.steps, "clocks": clocks, "sustained": sustained, "extra": extra,
         }
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 

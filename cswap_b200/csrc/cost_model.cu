@@ -232,8 +232,12 @@ struct Cand {
 // finished and not before the link is free; if copy + decode end after the
 // tensor is needed, backward stalls and everything later shifts.  Returns the
 // total stall and writes the per-tensor stalls.
+// With `take_back`, a losslessly swapped tensor whose copy out has not finished
+// when backward asks for it is handed back as it is (what the Execution classes
+// do): no copy in and no stall for it - and no memory freed, which is why the
+// decision itself does not count on it.
 double simulate(const csw_cost_model* cm, const csw_tensor_desc* td, size_t n, const std::vector<Cand>& c,
-                double fwd_total, double* stalls) {
+                double fwd_total, double* stalls, bool take_back = false) {
   std::vector<double> on_host(n);
   double link = 0;
   for (size_t i = 0; i < n; i++) {
@@ -247,6 +251,10 @@ double simulate(const csw_cost_model* cm, const csw_tensor_desc* td, size_t n, c
     if (stalls) stalls[j] = 0;
     if (c[j].policy == CSW_POLICY_KEEP) continue;
     const double need = fwd_total + td[j].need_s + stall;
+    if (take_back && (c[j].policy == CSW_POLICY_RAW || c[j].policy == CSW_POLICY_SPARSE) && on_host[j] > need) {
+      asked = std::max(asked, need);
+      continue;
+    }
     const double start = std::max(std::max(h2d, on_host[j]), asked);
     h2d = start + cm->h2d_a + c[j].moved / cm->h2d_bps;
     const double arrive = h2d + c[j].dec;
@@ -344,7 +352,7 @@ csw_status csw_cost_simulate(const csw_cost_model* cm, const csw_tensor_desc* td
       cur[i] = {CSW_POLICY_KEEP, 0, 0, 0, true};
   }
   std::vector<double> stalls(n ? n : 1);
-  *total_stall_s = simulate(cm, td, n, cur, fwd_total_s, stalls.data());
+  *total_stall_s = simulate(cm, td, n, cur, fwd_total_s, stalls.data(), /*take_back=*/true);
   if (exposed)
     for (size_t i = 0; i < n; i++) exposed[i] = stalls[i];
   return CSW_OK;

@@ -331,7 +331,10 @@ csw_status csw_cost_decide(const csw_cost_model* model, const csw_tensor_desc* t
 /* The same simulation for a policy vector the caller supplies (KEEP, RAW,
  * SPARSE or ZFP per tensor): each tensor's modelled stall to `exposed` (may be
  * NULL) and their sum to *total_stall_s.  A choice the tensor does not allow
- * (ZFP on fewer than 1024 values, SPARSE without a zero fraction) counts as RAW. */
+ * (ZFP on fewer than 1024 values, SPARSE without a zero fraction) counts as RAW.
+ * Unlike the decision, this prediction knows that a raw or sparse tensor whose
+ * copy out is still under way when backward asks for it is handed back as it
+ * is (no copy in, no stall - and no memory freed). */
 csw_status csw_cost_simulate(const csw_cost_model* model, const csw_tensor_desc* tensors, size_t n, double fwd_total_s,
                              const int* policy, double* exposed, double* total_stall_s);
 

@@ -82,6 +82,21 @@ def test_cost_decision_is_pure_host_logic(L):
     pol2, stall2 = cm.decide(small, 1e-3)
     assert pol2 == [2] * 5 and sum(stall2) == 0.0
     assert cm.decide([], 0.0) == ([], [])
+    # the prediction for a given table: keeping everything costs nothing, and raw tensors that backward
+    # wants before they have left are taken back (which is why all-raw can be predicted cheaper than a
+    # table with codecs in it: it frees no memory for those tensors either)
+    total_keep, _ = cm.simulate(tensors, [0] * 6, fwd)
+    total_dec, per = cm.simulate(tensors, pol, fwd)
+    total_raw, per_raw = cm.simulate(tensors, [2] * 6, fwd)
+    assert total_keep == 0.0 and total_dec > 0.0 and total_raw > 0.0 and len(per) == 6
+    # six 32 MiB copies queue on a 50 GB/s link: the last ones are still on their way out when backward
+    # (1 ms after the forward pass began) asks for them, so they stall nothing
+    assert per_raw[4] == 0.0 and per_raw[3] == 0.0 and per_raw[0] > 0.0
+    # the sparse slopes fitted at 75 % / 90 % zeros are used for a tensor that sparse: with a codec that is
+    # hopeless there (but fine at 50 %) the 90 %-zero tensor stays raw
+    cm2 = cs.CostModel(**cm.as_dict())
+    cm2.c.sparse_enc_b75, cm2.c.sparse_enc_b90, cm2.c.sparse_dec_b75, cm2.c.sparse_dec_b90 = 2e-13, 1e-9, 1.5e-13, 1e-9
+    assert cm2.decide(tensors, fwd)[0][0] == 2
     with pytest.raises(cs.CswapError):
         cs.CostModel().decide([cs.TensorDesc(n)])  # no link bandwidth fitted
 
