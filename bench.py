@@ -789,6 +789,8 @@ def main():
     extra = {}
     if not args.no_extra:
         extra = side_measurements(cs, torch, dev, peak, world, args)
+        extra["speedup_over_reference_cuda"] = against_reference_cuda(extra.get("reference_cuda"), t_enc, t_dec,
+                                                                     extra["sparse"])
         # The two calls block, as the reference's do, so they cannot overlap each other: each is
         # bound by its larger direction (the field in, then the field out).  Against the measured
         # one-direction copy rates with every rank copying at once.
@@ -1034,6 +1036,25 @@ def side_measurements(cs, torch, dev, peak, world=1, args=None):
         out["reference_cuda"] = reference_cuda_times(args.mib if args else 256, args.rate if args else 8, dev)
     except Exception as err:  # the checker's build is optional
         out["reference_cuda"] = {"unavailable": repr(err)}
+    return out
+
+
+def against_reference_cuda(ref, t_enc, t_dec, sparse_rows):
+    """This library's kernels over the reference's own on the same GPU and
+    tensors (time ratios, > 1 means faster here)."""
+    if not ref or "zfp" not in ref:
+        return None
+    z = ref["zfp"]
+    out = {"zfp_encode": z["encode_ms"] * 1e-3 / t_enc, "zfp_decode": z["decode_ms"] * 1e-3 / t_dec,
+           "zfp_roundtrip": (z["encode_ms"] + z["decode_ms"]) * 1e-3 / (t_enc + t_dec)}
+    mine = {round(r["zero_fraction"], 1): r for r in sparse_rows if r["tensor_mib"] == 16}
+    n = 16 * 262144
+    for r in ref.get("sparse", []):
+        m = mine.get(round(r["zero_fraction"], 1))
+        if m:
+            key = f"sparse_{int(r['zero_fraction'] * 100)}"
+            out[key + "_compress"] = r["compress_ms"] * 1e-3 / (4 * n / m["onepass_compress_GBps_uncompressed"] / 1e9)
+            out[key + "_decompress"] = r["decompress_ms"] * 1e-3 / (4 * n / m["decompress_GBps_uncompressed"] / 1e9)
     return out
 
 

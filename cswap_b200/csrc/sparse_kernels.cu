@@ -72,82 +72,45 @@ sparse_count_kernel(const uint32_t* __restrict__ in, uint64_t n, uint32_t* __res
 }
 
 // ---- pass 2: exclusive scan of the tile counts (one CTA) --------------------------
+// One CTA of 1024 threads scans `len` counts: off[i] = sum of cnt[0 .. i-1], the
+// total to *total.  cnt and off may be the same array (each thread reads its own
+// element before it writes it), which is how the in-place callers use it.
+template <class T>
 __global__ void __launch_bounds__(1024)
-sparse_scan_kernel(uint32_t* __restrict__ tile_off, uint32_t ntiles, uint32_t* __restrict__ nnz_out) {
-  __shared__ uint32_t warp_sum[32];
-  __shared__ uint32_t carry_s;
+block_exclusive_scan_kernel(const T* cnt, T* off, uint32_t len, T* __restrict__ total) {
+  __shared__ T warp_sum[32];
+  __shared__ T carry_s;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (threadIdx.x == 0) carry_s = 0;
   __syncthreads();
-  for (uint32_t base = 0; base < ntiles; base += 1024) {
+  for (uint32_t base = 0; base < len; base += 1024) {
     const uint32_t i = base + threadIdx.x;
-    const uint32_t c = i < ntiles ? tile_off[i] : 0u;
-    uint32_t x = c;
+    const T c = i < len ? cnt[i] : T(0);
+    T x = c;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
-      const uint32_t y = __shfl_up_sync(0xffffffffu, x, d);
+      const T y = __shfl_up_sync(0xffffffffu, x, d);
       if (lane >= d) x += y;
     }
     if (lane == 31) warp_sum[warp] = x;
     __syncthreads();
     if (warp == 0) {
-      uint32_t s = warp_sum[lane];
+      T s = warp_sum[lane];
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {
-        const uint32_t y = __shfl_up_sync(0xffffffffu, s, d);
+        const T y = __shfl_up_sync(0xffffffffu, s, d);
         if (lane >= d) s += y;
       }
       warp_sum[lane] = s;  // inclusive
     }
     __syncthreads();
-    const uint32_t carry = carry_s;
-    const uint32_t before = carry + (warp ? warp_sum[warp - 1] : 0u) + x - c;
-    if (i < ntiles) tile_off[i] = before;
+    const T carry = carry_s;
+    if (i < len) off[i] = carry + (warp ? warp_sum[warp - 1] : T(0)) + x - c;
     __syncthreads();
     if (threadIdx.x == 1023) carry_s = carry + warp_sum[31];
     __syncthreads();
   }
-  if (threadIdx.x == 0) *nnz_out = carry_s;
-}
-
-// Same scan with the counts read from one array and the exclusive offsets
-// written to another (the counts stay untouched).
-__global__ void __launch_bounds__(1024)
-sparse_scan_split_kernel(const uint32_t* __restrict__ tile_cnt, uint32_t* __restrict__ tile_off, uint32_t ntiles,
-                         uint32_t* __restrict__ nnz_out) {
-  __shared__ uint32_t warp_sum[32];
-  __shared__ uint32_t carry_s;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (threadIdx.x == 0) carry_s = 0;
-  __syncthreads();
-  for (uint32_t base = 0; base < ntiles; base += 1024) {
-    const uint32_t i = base + threadIdx.x;
-    const uint32_t c = i < ntiles ? tile_cnt[i] : 0u;
-    uint32_t x = c;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      const uint32_t y = __shfl_up_sync(0xffffffffu, x, d);
-      if (lane >= d) x += y;
-    }
-    if (lane == 31) warp_sum[warp] = x;
-    __syncthreads();
-    if (warp == 0) {
-      uint32_t s = warp_sum[lane];
-#pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        const uint32_t y = __shfl_up_sync(0xffffffffu, s, d);
-        if (lane >= d) s += y;
-      }
-      warp_sum[lane] = s;
-    }
-    __syncthreads();
-    const uint32_t carry = carry_s;
-    if (i < ntiles) tile_off[i] = carry + (warp ? warp_sum[warp - 1] : 0u) + x - c;
-    __syncthreads();
-    if (threadIdx.x == 1023) carry_s = carry + warp_sum[31];
-    __syncthreads();
-  }
-  if (threadIdx.x == 0) *nnz_out = carry_s;
+  if (threadIdx.x == 0) *total = carry_s;
 }
 
 // ---- pass 3: pack the non-zeros ----------------------------------------------------
@@ -294,45 +257,6 @@ legacy_count_kernel(const uint32_t* __restrict__ in, int n, int chunk, int worke
   if (lane == 0) count[i] = cnt;
 }
 
-// In-place exclusive scan of the first `len` counts, total to num[0]
-// (compression.cu:9-19), one CTA.
-__global__ void __launch_bounds__(1024)
-legacy_scan_kernel(int* __restrict__ idx, int len, int* __restrict__ num) {
-  __shared__ int warp_sum[32];
-  __shared__ int carry_s;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (threadIdx.x == 0) carry_s = 0;
-  __syncthreads();
-  for (int base = 0; base < len; base += 1024) {
-    const int i = base + threadIdx.x;
-    const int c = i < len ? idx[i] : 0;
-    int x = c;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      const int y = __shfl_up_sync(0xffffffffu, x, d);
-      if (lane >= d) x += y;
-    }
-    if (lane == 31) warp_sum[warp] = x;
-    __syncthreads();
-    if (warp == 0) {
-      int s = warp_sum[lane];
-#pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        const int y = __shfl_up_sync(0xffffffffu, s, d);
-        if (lane >= d) s += y;
-      }
-      warp_sum[lane] = s;
-    }
-    __syncthreads();
-    const int carry = carry_s;
-    if (i < len) idx[i] = carry + (warp ? warp_sum[warp - 1] : 0) + x - c;
-    __syncthreads();
-    if (threadIdx.x == 1023) carry_s = carry + warp_sum[31];
-    __syncthreads();
-  }
-  if (threadIdx.x == 0) num[0] = carry_s;
-}
-
 __global__ void __launch_bounds__(kThreads)
 legacy_pack_kernel(const uint32_t* __restrict__ in, int n, int chunk, int workers, uint32_t* __restrict__ values,
                    const int* __restrict__ begin, uint32_t* __restrict__ bitmap) {
@@ -390,7 +314,7 @@ cudaError_t sparse_compress_launch(const float* in, uint64_t n, uint32_t* bitmap
   if (ntiles) {
     sparse_count_kernel<<<ntiles, kThreads, 0, stream>>>(reinterpret_cast<const uint32_t*>(in), n, bitmap, tile_off);
   }
-  sparse_scan_kernel<<<1, 1024, 0, stream>>>(tile_off, ntiles, nnz_out);
+  block_exclusive_scan_kernel<uint32_t><<<1, 1024, 0, stream>>>(tile_off, tile_off, ntiles, nnz_out);
   if (ntiles) {
     sparse_pack_kernel<<<ntiles, kThreads, 0, stream>>>(reinterpret_cast<const uint32_t*>(in), n, tile_off,
                                                         reinterpret_cast<uint32_t*>(values));
@@ -406,7 +330,7 @@ cudaError_t sparse_compress_scratch_launch(const float* in, uint64_t n, uint32_t
     sparse_count_kernel<<<ntiles, kThreads, 0, stream>>>(reinterpret_cast<const uint32_t*>(in), n, bitmap,
                                                          tile_cnt_scratch);
   }
-  sparse_scan_split_kernel<<<1, 1024, 0, stream>>>(tile_cnt_scratch, tile_off, ntiles, nnz_out);
+  block_exclusive_scan_kernel<uint32_t><<<1, 1024, 0, stream>>>(tile_cnt_scratch, tile_off, ntiles, nnz_out);
   if (ntiles) {
     sparse_pack_kernel<<<ntiles, kThreads, 0, stream>>>(reinterpret_cast<const uint32_t*>(in), n, tile_off,
                                                         reinterpret_cast<uint32_t*>(values));
@@ -444,7 +368,8 @@ cudaError_t legacy_count_launch(int n, int workers, const float* in, int* count,
 }
 cudaError_t legacy_scan_launch(int* idx, int len, int* num, cudaStream_t stream) {
   if (len <= 0) return cudaSuccess;
-  legacy_scan_kernel<<<1, 1024, 0, stream>>>(idx, len, num);
+  // in-place scan of the first `len` counts, total to num[0] (compression.cu:9-19)
+  block_exclusive_scan_kernel<int><<<1, 1024, 0, stream>>>(idx, idx, (uint32_t)len, num);
   return cudaGetLastError();
 }
 cudaError_t legacy_pack_launch(int n, int workers, const float* in, float* values, const int* begin, uint32_t* bitmap,

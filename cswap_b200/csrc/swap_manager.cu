@@ -151,6 +151,7 @@ struct csw_mgr {
   std::vector<cudaEvent_t> free_events;
   std::vector<csw_ticket*> live;      // tickets whose staging may be reclaimable
   std::vector<csw_ticket*> zombies;   // released tickets whose copies are still in flight
+  std::vector<csw_ticket*> all;       // every ticket not yet destroyed (so that destroy can free what callers kept)
   csw_mgr_stats stats{};
   std::mutex mu;
 };
@@ -216,6 +217,12 @@ void destroy_ticket(csw_mgr* m, csw_ticket* t) {
   put_event(m, t->ev_d2h);
   put_event(m, t->ev_h2d);
   put_event(m, t->ev_done);
+  for (size_t i = 0; i < m->all.size(); i++)
+    if (m->all[i] == t) {
+      m->all[i] = m->all.back();
+      m->all.pop_back();
+      break;
+    }
   delete t;
 }
 
@@ -337,8 +344,11 @@ csw_status csw_mgr_destroy(csw_mgr* m) {
   if (m->s_d2h) cudaStreamSynchronize(m->s_d2h);
   if (m->s_d2h_c) cudaStreamSynchronize(m->s_d2h_c);
   if (m->s_h2d) cudaStreamSynchronize(m->s_h2d);
-  for (csw_ticket* t : m->zombies) destroy_ticket(m, t);
+  // every ticket still alive, released or not: the streams are idle now, so all of it can go
+  // (handles the caller still holds are invalid once the manager is gone)
+  while (!m->all.empty()) destroy_ticket(m, m->all.back());
   m->zombies.clear();
+  m->live.clear();
   for (cudaEvent_t ev : m->free_events) cudaEventDestroy(ev);
   if (m->s_codec) cudaStreamDestroy(m->s_codec);
   if (m->s_d2h) cudaStreamDestroy(m->s_d2h);
@@ -476,6 +486,7 @@ csw_status csw_swap_out(csw_mgr* m, const float* d_ptr, size_t numel, int policy
   if (t->moved_final) m->stats.moved_bytes_out += t->moved;
   m->live.push_back(t);
   t->in_live = true;
+  m->all.push_back(t);
   *ticket = t;
   return CSW_OK;
 }
@@ -771,6 +782,7 @@ csw_status csw_blob_import(csw_mgr* m, const void* blob, size_t bytes, csw_ticke
     return CSW_ERR_NOMEM;
   }
   std::memcpy(t->host, static_cast<const char*>(blob) + sizeof h, t->moved);
+  m->all.push_back(t);
   *ticket = t;
   return CSW_OK;
 }
