@@ -468,12 +468,13 @@ def run_model_workload(args):
             "cost_model": cm.as_dict(),
         }
     mgr.close()
-    if args.workload == "vgg16":
-        del model
-        torch.cuda.empty_cache()
-        cpp = vgg16_cpp_block(torch, dev, world, rank, local)  # every rank runs it; rank 0 reports
-        if rank == 0:
-            line["cpp_host_side"] = cpp
+    del model
+    torch.cuda.empty_cache()
+    # the same workload through the C++ host side; every rank runs it, rank 0 reports
+    cpp = vgg16_cpp_block(torch, dev, world, rank, local) if args.workload == "vgg16" else \
+        cpp_step_block(torch, dev, world, rank, local, "bert_step", ["--steps", str(steps), "--warmup", str(warmup)])
+    if rank == 0:
+        line["cpp_host_side"] = cpp
     if rank == 0:
         emit(line)
     if world > 1:
@@ -517,25 +518,21 @@ def hidden_bytes_sweep(W, cs, torch, model, mgr, make_batch, prof, policy_of, t_
     return {"candidates": len(ids), "hidden_activation_bytes": hidden, "curve": curve}
 
 
-def vgg16_cpp_block(torch, dev, world, rank, local):
-    """The swapped VGG16 step through the C++ host side (cswap::Execution over
-    libtorch, tests/cpp/vgg16_step.cpp, the driver laid out like the
-    reference's vgg16-cifar10.cpp): every rank launches the binary on its own
-    GPU behind one barrier, so the ranks share the host link while they run.
-    Rank 0's line is reported, with each row's step time replaced by the
-    slowest rank's."""
+def cpp_step_block(torch, dev, world, rank, local, name, extra_args):
+    """Launch tests/cpp/<name> --bench on this rank's GPU (all ranks behind one
+    barrier), parse its JSON line and add the slowest rank's time to every row."""
     import subprocess
     import torch.distributed as dist
-    exe = os.path.join(ROOT, "tests", "cpp", "vgg16_step")
+    exe = os.path.join(ROOT, "tests", "cpp", name)
     if not os.path.exists(exe):
-        return {"unavailable": "tests/cpp/vgg16_step has not been built (python -m cswap_b200.build --cpp)"}
+        return {"unavailable": f"tests/cpp/{name} has not been built (python -m cswap_b200.build --cpp)"}
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    r = subprocess.run([exe, "--bench", "--device", str(local), "--seed", str(1 + rank)], capture_output=True,
-                       text=True, timeout=900)
+    r = subprocess.run([exe, "--bench", "--device", str(local), "--seed", str(1 + rank)] + list(extra_args),
+                       capture_output=True, text=True, timeout=1500)
     if r.returncode != 0:
-        return {"unavailable": f"vgg16_step exited {r.returncode}: {r.stderr[-300:]}"}
+        return {"unavailable": f"{name} exited {r.returncode}: {r.stderr[-300:]}"}
     d = json.loads(r.stdout.strip().splitlines()[-1])
     names = sorted(d["rows"])
     worst = max_over_ranks([d["rows"][k]["ms_per_step_median"] for k in names], dev)
@@ -543,6 +540,16 @@ def vgg16_cpp_block(torch, dev, world, rank, local):
         d["rows"][k]["ms_per_step_median_slowest_rank"] = w
     d["ranks_running"] = world
     return d
+
+
+def vgg16_cpp_block(torch, dev, world, rank, local):
+    """The swapped VGG16 step through the C++ host side (cswap::Execution over
+    libtorch, tests/cpp/vgg16_step.cpp, the driver laid out like the
+    reference's vgg16-cifar10.cpp): every rank launches the binary on its own
+    GPU behind one barrier, so the ranks share the host link while they run.
+    Rank 0's line is reported, with each row's step time also given for the
+    slowest rank."""
+    return cpp_step_block(torch, dev, world, rank, local, "vgg16_step", [])
 
 
 def vgg16_block(args, cs, torch, dev, world, rank):

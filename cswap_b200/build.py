@@ -53,7 +53,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
-CPP_DRIVERS = ("execution_driver", "vgg16_step")
+CPP_DRIVERS = ("execution_driver", "vgg16_step", "bert_step")
 
 
 def build_cpp_driver(force: bool = False, name: str = "execution_driver") -> str:

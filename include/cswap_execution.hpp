@@ -113,39 +113,54 @@ class Execution {
     order_.clear();
     by_storage_.clear();
     producers_.clear();
-    seen_.clear();
+    handles_.clear();
     poll();
   }
-  void postforward() { poll(); }
+  void postforward() {
+    producers_.clear();  // they hold their layers' inputs: nothing is dropped after the forward pass
+    handles_.clear();
+    poll();
+  }
 
   // Execution.h:65-133
   void pre(torch::Tensor& t, Layer_type layer_type = ACT) {
     index++;
-    seen_.clear();
-    note_input(t);
-    maybe_swap_out(t, layer_type);
+    maybe_swap_out(t, layer_type, 0);
     begin_profile();
   }
-  // Execution.h:135-212
-  void pre(std::vector<torch::Tensor> inputs, Layer_type layer_type = ACT) {
+  // Execution.h:135-212.  The braced form the reference's drivers use
+  // (`exe.pre({pre, target})`) binds to the initializer_list overload, whose
+  // backing array holds exactly one extra handle per tensor while the call runs;
+  // a vector passed by name holds none beyond the caller's own.
+  void pre(std::initializer_list<torch::Tensor> inputs, Layer_type layer_type = ACT) {
     index++;
-    seen_.clear();
-    for (auto& t : inputs) note_input(t);
-    for (auto& t : inputs) maybe_swap_out(t, layer_type);
+    for (auto& t : inputs) maybe_swap_out(t, layer_type, 1);
+    begin_profile();
+  }
+  void pre(const std::vector<torch::Tensor>& inputs, Layer_type layer_type = ACT) {
+    index++;
+    for (auto& t : inputs) maybe_swap_out(t, layer_type, 0);
     begin_profile();
   }
   // Execution.h:217-310.  `producer`, when given, is the layer itself: what
   // rebuilds x from pre_t should x be dropped under policy 1.
   void post(torch::Tensor& pre_t, torch::Tensor& x, Layer_type layer_type = ACT, bool isomit = false,
             Producer producer = nullptr) {
-    torch::Tensor* in[1] = {&pre_t};
-    finish_layer(in, 1, x, layer_type, isomit, std::move(producer));
+    const torch::Tensor* in[1] = {&pre_t};
+    finish_layer(in, 1, 0, x, layer_type, isomit, std::move(producer));
   }
   // Execution.h:311-401
-  void post(std::vector<torch::Tensor> inputs, torch::Tensor& x, Layer_type layer_type = ACT, bool isomit = false) {
-    std::vector<torch::Tensor*> in;
+  void post(std::initializer_list<torch::Tensor> inputs, torch::Tensor& x, Layer_type layer_type = ACT,
+            bool isomit = false) {
+    std::vector<const torch::Tensor*> in;
     for (auto& t : inputs) in.push_back(&t);
-    finish_layer(in.data(), in.size(), x, layer_type, isomit, nullptr);
+    finish_layer(in.data(), in.size(), 1, x, layer_type, isomit, nullptr);
+  }
+  void post(const std::vector<torch::Tensor>& inputs, torch::Tensor& x, Layer_type layer_type = ACT,
+            bool isomit = false) {
+    std::vector<const torch::Tensor*> in;
+    for (auto& t : inputs) in.push_back(&t);
+    finish_layer(in.data(), in.size(), 0, x, layer_type, isomit, nullptr);
   }
 
   // ---- self-tuning (call sites Execution.h:224-233, resnet-cifar10.cpp:407-437) ----
@@ -183,7 +198,7 @@ class Execution {
   }
 
   // Fill policy / begin_stage from a profiled iteration.  Tensor id i (the
-  // output of layer i) becomes a swap candidate at the first layer that
+  // output of layer i) becomes a swap candidate at the last layer that
   // consumes it; the cost model gets the forward time at which that consumer
   // starts and the backward compute that precedes the consumer's backward
   // (bwd_factor times the forward time of the later layers) and simulates the
@@ -235,6 +250,15 @@ class Execution {
     return total + swaps * cost_model().host_swap_s;
   }
 
+  // begin_stage for every tensor id of a profiled iteration: the last layer that consumes it.
+  static std::map<int, int> last_consumers(const std::map<int, LayerProfile>& prof) {
+    std::map<int, int> last;
+    for (auto& kv : prof)
+      for (int tid : kv.second.inputs)
+        if (tid >= 0) last[tid] = kv.first;
+    return last;
+  }
+
   csw_mgr* manager() const { return mgr_; }
   csw_mgr_stats stats() const {
     csw_mgr_stats s{};
@@ -281,11 +305,6 @@ class Execution {
   struct Deferred {
     torch::Tensor t;
     int pol;
-  };
-  // How an input of the running layer looked when pre() saw it.
-  struct Seen {
-    const c10::TensorImpl* impl;
-    size_t impl_refs, storage_refs;
   };
 
   struct RestoreHook : torch::autograd::FunctionPreHook {
@@ -338,11 +357,13 @@ class Execution {
       start[i + 1] = start[i] + (it == prof.end() ? 0.0 : it->second.time_s);
     }
     c.fwd_total = start[c.n];
+    // a tensor is swapped at its LAST forward use (its storage is empty from then on), which is
+    // also the consumer whose backward runs first
     std::set<int> conv_inputs;
     for (auto& kv : prof)
       for (int tid : kv.second.inputs)
-        if (tid >= 0 && !c.consumer.count(tid)) {
-          c.consumer[tid] = kv.first;
+        if (tid >= 0) {
+          c.consumer[tid] = kv.first;  // prof is ordered by layer: the last one wins
           if (kv.second.type == CONV) conv_inputs.insert(tid);
         }
     const std::set<int>& lossy = lossy_ids ? *lossy_ids : conv_inputs;
@@ -393,7 +414,7 @@ class Execution {
     return pol;
   }
 
-  void maybe_swap_out(torch::Tensor& t, Layer_type layer_type) {
+  void maybe_swap_out(const torch::Tensor& t, Layer_type layer_type, size_t call_copies) {
     const int id = id_of(t);
     if (id < 0 || id >= (int)begin_stage.size() || index != begin_stage[id] || !t.grad_fn()) return;
     const int pol = effective_policy(id, layer_type);
@@ -406,11 +427,34 @@ class Execution {
     }
     if (pol == CSW_POLICY_DROP && !producers_.count(t.unsafeGetTensorImpl()))
       return;  // without its producer the tensor simply stays
-    // storage references beyond the tensor itself mean that its producer kept it for backward
-    // (a ReLU keeps its result): it will be needed again, so the copy out can start now and
-    // overlap with the consumer
-    if (t.storage().use_count() > 1) start_swap(t, pol);
+    // kept by its producer (a ReLU keeps its own result): it will be needed again, so the copy
+    // out can start now and overlap with the layer about to run.  Otherwise decide in post().
+    if (producer_kept(t)) start_swap(t, pol);
     else deferred_.push_back(Deferred{t, pol});
+  }
+
+  // Autograd adds a reference to the storage when a producer saves its own
+  // result (it keeps a detached alias of it).
+  bool producer_kept(const torch::Tensor& t) const {
+    auto own = by_storage_.find(t.storage().unsafeGetStorageImpl());
+    return t.storage().use_count() > 1 + ((own != by_storage_.end() && !own->second.expired()) ? 1u : 0u);
+  }
+
+  // Does anything hold `t` for backward?  Asked from post(), after the consumer
+  // has run.  A consumer that saves its input adds a reference to the TensorImpl.
+  // What the driver itself holds is what it held when the tensor came out of its
+  // producer's post(): the reference's drivers hold a layer output through `x`
+  // then, and through `pre` (with `x` overwritten) when its consumer's post() runs
+  // (vgg16-cifar10.cpp:219-226) - one handle either time; a driver that keeps
+  // every activation in a variable of its own holds one as well.  `copies` are the
+  // handles this class and the running call have added.  For a tensor that did not
+  // come out of a wrapped layer nothing is known, and the answer is "held", which
+  // costs a copy, never correctness.
+  bool held_for_backward(const torch::Tensor& t, size_t copies) const {
+    if (producer_kept(t)) return true;
+    auto h = handles_.find(t.unsafeGetTensorImpl());
+    if (h == handles_.end()) return true;
+    return t.use_count() - copies > h->second;
   }
 
   // Policy 1: nothing is copied; the storage is emptied after the consumer has
@@ -423,33 +467,13 @@ class Execution {
     s->storage = c10::intrusive_ptr<c10::StorageImpl>::reclaim_copy(t.storage().unsafeGetStorageImpl());
     s->nbytes = t.storage().nbytes();
     s->policy = CSW_POLICY_DROP;
-    s->producer = it->second.first;
-    s->producer_input = it->second.second;
+    s->producer = std::move(it->second.first);
+    s->producer_input = std::move(it->second.second);
+    producers_.erase(it);
     s->started = true;
     by_storage_[s->storage.get()] = s;
     pending_.push_back(s);
     dropped++;
-  }
-
-  void note_input(const torch::Tensor& t) {
-    if (t.defined() && t.has_storage())
-      seen_.push_back(Seen{t.unsafeGetTensorImpl(), t.use_count(), t.storage().use_count()});
-  }
-
-  // Does anything hold `t` for backward now that its consumer has run?  Called
-  // from post() with the same handles in existence as in pre() (`own` counts the
-  // copies this class has made since).  Autograd adds a reference to the
-  // TensorImpl when a consumer saves its input and to the storage when a
-  // producer saves its own result.  The reference's drivers alias the tensor
-  // through `pre` and `x` when pre() runs and through `pre` alone when post()
-  // runs (vgg16-cifar10.cpp:219-226), so an unchanged count means one new
-  // holder.  With drivers that hold their handles differently the answer errs
-  // towards "held", which costs a copy, never correctness.
-  bool held_for_backward(const torch::Tensor& t, size_t own) const {
-    if (t.storage().use_count() > 1 + (by_storage_.count(t.storage().unsafeGetStorageImpl()) ? 1 : 0)) return true;
-    for (auto& sn : seen_)
-      if (sn.impl == t.unsafeGetTensorImpl()) return t.use_count() - own >= sn.impl_refs;
-    return true;
   }
 
   void start_swap(const torch::Tensor& t, int pol) {
@@ -482,9 +506,10 @@ class Execution {
   // The layer has run: give the result its id, decide the deferred swaps, let
   // go of the swapped inputs' device blocks and arrange for their return before
   // the result's backward.
-  void finish_layer(torch::Tensor* const* inputs, size_t n_in, torch::Tensor& x, Layer_type layer_type, bool isomit,
-                    Producer producer) {
+  void finish_layer(const torch::Tensor* const* inputs, size_t n_in, size_t call_copies, torch::Tensor& x,
+                    Layer_type layer_type, bool isomit, Producer producer) {
     ids_[x.unsafeGetTensorImpl()] = index;
+    handles_[x.unsafeGetTensorImpl()] = x.use_count();  // what the driver itself holds of this output
     auto fn = x.grad_fn();
     if (profile) {
       ProfEntry& e = prof_[index];
@@ -503,13 +528,13 @@ class Execution {
         // does anything hold this consumed tensor for backward now that its consumer has run?
         if (tid >= 0 && inputs[i]->defined() && inputs[i]->is_cuda()) {
           auto pit = prof_.find(tid);
-          if (pit != prof_.end()) pit->second.p.saved = held_for_backward(*inputs[i], 0);
+          if (pit != prof_.end()) pit->second.p.saved = held_for_backward(*inputs[i], call_copies);
         }
       }
     }
     for (auto& d : deferred_) {
       const bool view = x.storage().unsafeGetStorageImpl() == d.t.storage().unsafeGetStorageImpl();
-      const bool saved = !view && held_for_backward(d.t, 1);
+      const bool saved = !view && held_for_backward(d.t, call_copies + 1);  // + the handle `d` holds
       if (saved && fn) start_swap(d.t, d.pol);
       else if (!saved && !view) skipped_unsaved++;
     }
@@ -550,7 +575,7 @@ class Execution {
       csw_swap_out_done(mgr_, s.ticket, &done);
       if (!done) {
         s.storage->set_data_ptr_noswap(std::move(s.reading));
-        s.restored = true;
+        settle(s);
         reclaimed++;
         poll();
         return;
@@ -567,11 +592,12 @@ class Execution {
       check(csw_swap_in(mgr_, s.ticket, static_cast<float*>(dp.get()), stream), "csw_swap_in");
       s.storage->set_data_ptr_noswap(std::move(dp));
     }
-    s.restored = true;
+    const int order = s.order;
+    settle(s);
     // One step ahead: start bringing back - copy AND decode, into a block taken now - the
     // tensor swapped out just before this one, so that its consumer's backward finds it
     // ready instead of waiting for a decode that starts only when it asks.
-    for (int i = s.order - 1; i >= 0; i--) {
+    for (int i = order - 1; i >= 0; i--) {
       auto p = order_[i].lock();
       if (p && !p->restored && p->ticket) {
         int done = 1;
@@ -606,21 +632,42 @@ class Execution {
       throw std::runtime_error("cswap: recomputed activation does not match the dropped one");
     auto* os = out.storage().unsafeGetStorageImpl();
     s.storage->set_data_ptr_noswap(os->set_data_ptr(at::DataPtr(nullptr, os->device())));
-    s.restored = true;
+    settle(s);
     recomputed++;
+  }
+
+  // The tensor is back.  The restore hooks keep this record alive until the
+  // graph is destroyed, so everything it holds is let go here: with its own
+  // reference to the storage gone, the block is freed as soon as the backward
+  // nodes that saved the tensor have run; the ticket's host memory returns to the
+  // pool once its copy has finished (csw_ticket_release never blocks).
+  void settle(Swapped& s) {
+    s.restored = true;
+    s.storage.reset();
+    if (s.reading.get() == nullptr) release_ticket(s);  // else poll() does, once the block has been read
+    s.producer = nullptr;
+    s.producer_input = torch::Tensor();
   }
 
   // free device blocks whose swap-out has finished reading them (never blocks)
   void poll() {
     size_t k = 0;
     for (auto& s : reading_) {
+      if (s->reading.get() == nullptr) continue;  // taken back: the storage owns the block again
       int done = 1;
-      if (s->restored && s->reading.get() == nullptr) continue;  // taken back: the storage owns the block again
       if (s->ticket) csw_swap_out_done(mgr_, s->ticket, &done);
-      if (done) s->reading.clear();
-      else reading_[k++] = s;
+      if (done) {
+        s->reading.clear();
+        if (s->restored) release_ticket(*s);
+      } else {
+        reading_[k++] = s;
+      }
     }
     reading_.resize(k);
+  }
+  void release_ticket(Swapped& s) {
+    if (s.ticket) csw_ticket_release(mgr_, s.ticket);
+    s.ticket = nullptr;
   }
   void drain() {
     for (auto& s : reading_)
@@ -642,7 +689,7 @@ class Execution {
   std::unordered_map<const c10::StorageImpl*, std::weak_ptr<Swapped>> by_storage_;
   std::vector<std::shared_ptr<Swapped>> pending_;  // swap-outs started by the current pre()
   std::vector<Deferred> deferred_;                 // swaps waiting for their consumer to have run
-  std::vector<Seen> seen_;                         // the running layer's inputs as pre() found them
+  std::unordered_map<const c10::TensorImpl*, size_t> handles_;  // driver handles per wrapped layer output
   std::vector<std::shared_ptr<Swapped>> reading_;  // device blocks still being read
   std::vector<std::weak_ptr<Swapped>> order_;      // this step's swap-outs, in order
   std::map<int, ProfEntry> prof_;
