@@ -96,6 +96,21 @@ CSW_HD bool warp_all(bool p) {
   return p;
 #endif
 }
+// smallest value over the lanes of the warp, all of which must call (host: the one "lane")
+CSW_HD int warp_min(int v) {
+#if defined(__CUDA_ARCH__)
+  return __reduce_min_sync(0xffffffffu, v);
+#else
+  return v;
+#endif
+}
+CSW_HD int ctz32(uint32_t x) {  // x != 0
+#if defined(__CUDA_ARCH__)
+  return __ffs((int)x) - 1;
+#else
+  return __builtin_ctz(x);
+#endif
+}
 CSW_HD uint32_t low_mask32(int n) {  // n in 0..32
   return n >= 32 ? 0xffffffffu : ((1u << n) - 1u);
 }
@@ -877,13 +892,25 @@ template <class WordSrc>
 CSW_HD void decode_block3_pos(const WordSrc& src, int maxbits, float (&f)[64], const uint32_t* dec_lut,
                               const PipeConsts& kc) {
   const uint32_t head = src.word(0);
+  // While no coefficient is significant a plane is a single '0' bit (the group
+  // test of decode.cuh:147 fails at n = 0), so the zeros that follow the header
+  // are whole planes.  The count common to the warp is skipped in one go; a
+  // lane's further empty planes go through the loop below like any other.
+  int lead = 32;
+  if (head & 1u) {
+    const uint32_t first = funnel_r(head, src.word(1), 9);  // stream bits 9..40
+    lead = first ? ctz32(first) : 32;
+    const int budget = maxbits - 9;
+    lead = lead < budget ? lead : budget;
+  }
+  lead = warp_min(lead);  // every lane of the warp is here: the tile test before the call is warp-uniform
   if (!(head & 1u)) {  // zero block
 #pragma unroll
     for (int i = 0; i < 64; i++) f[i] = 0.0f;
     return;
   }
   const uint32_t e = (head >> 1) & 0xffu;
-  int pos = 9, n = 0;
+  int pos = 9 + lead, n = 0;
   uint32_t u[64];
   // u holds coefficient ^ 0xaaaaaaaa throughout (planes never decoded are zero, i.e. 0xaa bytes)
 #pragma unroll
@@ -893,6 +920,11 @@ CSW_HD void decode_block3_pos(const WordSrc& src, int maxbits, float (&f)[64], c
 #pragma unroll
     for (int k = 7; k >= 0; k--) {
       uint32_t xl = 0u, xh = 0u;
+      if (31 - (8 * c + k) < lead) {  // one of the skipped leading planes (warp-uniform)
+        lo[k] = 0u;
+        hi[k] = 0u;
+        continue;
+      }
       if (pos < maxbits) {
         // first min(n, budget) bits verbatim (decode.cuh:143-145)
         const int left0 = maxbits - pos;
