@@ -324,21 +324,27 @@ constexpr CSW_HD uint32_t enc_lut_entry(uint32_t v) {
   return pat | ((uint32_t)len << 16) | (lf << 24);
 }
 
-// Decoder: entry for (limit L in 1..8, state, next stream byte).  Simulates the
+// Decoder: entry for (limit L in 0..8, state, next stream byte).  Simulates the
 // group-test parser of decode.cuh:147-164 over at most L stream bits.
 // State 0: expecting a group-test bit; state 1: inside a unary run (expecting
 // value bits until a one); state 2: negative group test seen, plane finished.
+// L = 0 (no open position left, or the budget is spent) finishes the plane
+// without reading: from state 1 the run's final one is implied.
 // One field per byte, so that each is a single byte-permute away:
 // byte 0: stream bits consumed; byte 1: positions advanced;
 // byte 2: plane bits found, relative to the starting position;
 // byte 3: state afterwards.
-constexpr int DEC_LUT_SIZE = 8 * 2 * 256;
-constexpr CSW_HD int dec_lut_index(int L, int state, uint32_t byte) { return ((L - 1) * 2 + state) * 256 + (int)byte; }
+constexpr int DEC_LUT_SIZE = 9 * 2 * 256;
+constexpr CSW_HD int dec_lut_index(int L, int state, uint32_t byte) { return (L * 2 + state) * 256 + (int)byte; }
 constexpr CSW_HD uint32_t dec_lut_entry(int idx) {
   uint32_t byte = idx & 255;
-  int st = (idx >> 8) & 1, L = (idx >> 9) + 1;
+  int st = (idx >> 8) & 1, L = idx >> 9;
   int c = 0, dn = 0;
   uint32_t pat = 0;
+  if (L == 0) {
+    if (st == 1) { pat = 1u; dn = 1; }
+    st = 2;
+  }
   while (c < L) {
     uint32_t bit = (byte >> c) & 1u;
     c++;
@@ -888,20 +894,76 @@ CSW_HD void inv_order3_sub(const uint32_t (&u)[64], int (&v)[64], uint32_t nb, i
                            std::integer_sequence<int, I...>) {
   ((v[PermAt<3, I>::v] = imad((int)nb, mone, (int)u[I])), ...);  // u - 0xaaaaaaaa on the multiply-add pipe
 }
+// Planes 8c+7 .. 8c of one block: (hi[k]:lo[k]) <- plane 8c+k, odd planes
+// complemented (the xor half of the inverse negabinary map, applied to planes
+// instead of coefficients).  `skip` leading planes of the slice are known to be
+// empty and have been stepped over already (warp-uniform).
+template <class WordSrc>
+CSW_HD void decode_slice3(const WordSrc& src, int maxbits, const uint32_t* dec_lut, int skip, int& pos, int& n,
+                          uint32_t (&lo)[8], uint32_t (&hi)[8]) {
+#pragma unroll
+  for (int k = 7; k >= 0; k--) {
+    uint32_t xl = 0u, xh = 0u;
+    if (7 - k >= skip && pos < maxbits) {
+      // first min(n, budget) bits verbatim (decode.cuh:143-145)
+      const int left0 = maxbits - pos;
+      const int m = n < left0 ? n : left0;
+      const int w = pos >> 5;
+      const uint32_t w0 = src.word(w), w1 = src.word(w + 1), w2 = src.word(w + 2);
+      xl = funnel_r(w0, w1, pos) & low_mask_sat(m);
+      xh = funnel_r(w1, w2, pos) & low_mask_sat(m - 32);
+      pos += m;
+      // group tests and unary runs (decode.cuh:147-164), up to eight stream
+      // bits per step; none once every coefficient is significant.  The bits
+      // found are gathered in (ah:al), kept rotated so that position n is bit
+      // 0: a step ORs its pattern in at the bottom and rotates by the positions
+      // it advanced.
+      if (n < 64) {
+        uint32_t al = 0u, ah = 0u;
+        int st = 0;
+        do {
+          // stream bits this step may read: up to eight, no further than the
+          // last open position (a run's final one is implied, so it stops one
+          // short) and no further than the block's budget; none at all ends
+          // the plane through the table's L = 0 rows
+          const int left = maxbits - pos;
+          const int lim = 64 - st - n;
+          int L = lim < 8 ? lim : 8;
+          L = left < L ? left : L;
+          const uint32_t en = dec_lut[dec_lut_index(L, st, peek_at(src, pos) & 0xffu)];
+          const int dn = dec_lut_advance(en);
+          al |= dec_lut_pattern(en);
+          ror64_small(al, ah, dn);
+          n += dn;
+          pos += dec_lut_used(en);
+          st = dec_lut_state(en);
+        } while (st != 2);
+        rol64(al, ah, n);  // position 0 back to bit 0
+        xl |= al;
+        xh |= ah;
+      }
+    }
+    lo[k] = (k & 1) ? ~xl : xl;
+    hi[k] = (k & 1) ? ~xh : xh;
+  }
+}
+
 template <class WordSrc>
 CSW_HD void decode_block3_pos(const WordSrc& src, int maxbits, float (&f)[64], const uint32_t* dec_lut,
                               const PipeConsts& kc) {
   const uint32_t head = src.word(0);
   // While no coefficient is significant a plane is a single '0' bit (the group
   // test of decode.cuh:147 fails at n = 0), so the zeros that follow the header
-  // are whole planes.  The count common to the warp is skipped in one go; a
-  // lane's further empty planes go through the loop below like any other.
-  int lead = 32;
+  // are whole planes.  The count common to the warp (at most the first slice)
+  // is skipped in one go; a lane's further empty planes go through the loop
+  // like any other.
+  int lead = 8;
   if (head & 1u) {
     const uint32_t first = funnel_r(head, src.word(1), 9);  // stream bits 9..40
-    lead = first ? ctz32(first) : 32;
+    const int zeros = first ? ctz32(first) : 32;
     const int budget = maxbits - 9;
-    lead = lead < budget ? lead : budget;
+    lead = zeros < lead ? zeros : lead;
+    lead = budget < lead ? budget : lead;
   }
   lead = warp_min(lead);  // every lane of the warp is here: the tile test before the call is warp-uniform
   if (!(head & 1u)) {  // zero block
@@ -911,78 +973,21 @@ CSW_HD void decode_block3_pos(const WordSrc& src, int maxbits, float (&f)[64], c
   }
   const uint32_t e = (head >> 1) & 0xffu;
   int pos = 9 + lead, n = 0;
-  uint32_t u[64];
-  // u holds coefficient ^ 0xaaaaaaaa throughout (planes never decoded are zero, i.e. 0xaa bytes)
+  uint32_t u[64], lo[8], hi[8];
+  // u holds coefficient ^ 0xaaaaaaaa throughout: planes never decoded are zero, i.e. 0xaa bytes.
+  // The first slice is peeled so that these constants are operands of its byte permutes
+  // instead of sixty-four register initialisations carried into a loop.
+  decode_slice3(src, maxbits, dec_lut, lead, pos, n, lo, hi);
 #pragma unroll
   for (int i = 0; i < 64; i++) u[i] = 0xaaaaaaaau;
-  for (int c = 3; c >= 0; c--) {
-    uint32_t lo[8], hi[8];
-#pragma unroll
-    for (int k = 7; k >= 0; k--) {
-      uint32_t xl = 0u, xh = 0u;
-      if (31 - (8 * c + k) < lead) {  // one of the skipped leading planes (warp-uniform)
-        lo[k] = 0u;
-        hi[k] = 0u;
-        continue;
-      }
-      if (pos < maxbits) {
-        // first min(n, budget) bits verbatim (decode.cuh:143-145)
-        const int left0 = maxbits - pos;
-        const int m = n < left0 ? n : left0;
-        const int w = pos >> 5;
-        const uint32_t w0 = src.word(w), w1 = src.word(w + 1), w2 = src.word(w + 2);
-        xl = funnel_r(w0, w1, pos) & low_mask_sat(m);
-        xh = funnel_r(w1, w2, pos) & low_mask_sat(m - 32);
-        pos += m;
-        // group tests and unary runs (decode.cuh:147-164), up to eight stream
-        // bits per step.  The bits found are gathered in (ah:al), kept rotated
-        // so that position n is bit 0: a step ORs its pattern in at the bottom
-        // and rotates by the positions it advanced.
-        uint32_t al = 0u, ah = 0u;
-        int st = 0;
-        for (;;) {
-          // stream bits this step may read: up to eight, no further than the
-          // last open position (a run's final one is implied, so it stops one
-          // short) and no further than the block's budget
-          const int left = maxbits - pos;
-          const int lim = 64 - st - n;
-          int L = lim < 8 ? lim : 8;
-          L = left < L ? left : L;
-          if (L <= 0) {
-            if (st == 1) {  // run cut short: the one is implied
-              al |= 1u;
-              ror64_small(al, ah, 1);
-              n++;
-            }
-            break;
-          }
-          const uint32_t en = dec_lut[dec_lut_index(L, st, peek_at(src, pos) & 0xffu)];
-          const int dn = dec_lut_advance(en);
-          al |= dec_lut_pattern(en);
-          ror64_small(al, ah, dn);
-          n += dn;
-          pos += dec_lut_used(en);
-          st = dec_lut_state(en);
-          if (st == 2) break;
-        }
-        rol64(al, ah, n);  // position 0 back to bit 0
-        xl |= al;
-        xh |= ah;
-      }
-      lo[k] = xl;
-      hi[k] = xh;
-    }
+  bytes_from_planes<0>(lo, 0x4210u, 0x1000u, u);
+  bytes_from_planes<1>(hi, 0x4210u, 0x1000u, u);
+  for (int c = 2; c >= 0 && pos < maxbits; c--) {
+    decode_slice3(src, maxbits, dec_lut, 0, pos, n, lo, hi);
     const uint32_t sel0 = (0x3210u & ~(0xfu << (4 * c))) | (4u << (4 * c));
     const uint32_t step = 1u << (4 * c);
-    // the xor half of the inverse negabinary map, applied to planes instead of coefficients
-#pragma unroll
-    for (int k = 1; k < 8; k += 2) {
-      lo[k] = ~lo[k];
-      hi[k] = ~hi[k];
-    }
     bytes_from_planes<0>(lo, sel0, step, u);
     bytes_from_planes<1>(hi, sel0, step, u);
-    if (pos >= maxbits) break;
   }
   int v[64];
   inv_order3_sub(u, v, kc.nb, kc.mone, std::make_integer_sequence<int, 64>{});
