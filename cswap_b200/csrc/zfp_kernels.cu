@@ -16,7 +16,12 @@
 //    Measured against a persistent variant that pulled each group with a bulk
 //    async copy into a shared tile and wrote the stream through a transposing
 //    copy-out: the extra shared-memory hop, its barriers and the registers of
-//    the persistent loop cost 40 % at 256 MiB (177 against 125 us).
+//    the persistent loop cost 40 % at 256 MiB (177 against 125 us).  A second
+//    persistent encoder, whose lanes fetched their next block with 16-byte
+//    asynchronous copies into slots of their own while coding (no barrier),
+//    took 168 us (32 KB more shared memory per CTA, 196 bytes of spills, and
+//    the CTAs of an SM marching through the same phase together); asking L2
+//    for the successor CTA's lines ahead of time cost 3 % in either kernel.
 //  * generic kernels, one thread per block straight from/to global memory, for
 //    any 1-D/2-D/3-D extents, strides, partial blocks and bit budgets.
 //
@@ -60,6 +65,18 @@ struct SmemStage {
     return q[(slot * QUEUE_FIELDS + field) * kThreads];
   }
 };
+
+// The expansion table, evaluated at compile time: a CTA copies it to shared
+// memory (two words per thread) instead of computing 256 entries per launch.
+struct EncTable {
+  uint32_t v[ENC_LUT_SIZE];
+};
+constexpr EncTable make_enc_table() {
+  EncTable t{};
+  for (int i = 0; i < ENC_LUT_SIZE; i++) t.v[i] = enc_lut_entry((uint32_t)i);
+  return t;
+}
+__device__ const EncTable g_enc_table = make_enc_table();
 
 // z-slab that feeds row z of a block with vz valid slabs (encode.cuh:17-38
 // applied along z: a,a,a,a / a,b,b,a / a,b,c,a)
@@ -105,7 +122,7 @@ zfp_encode_slab_kernel(const float* __restrict__ in, uint32_t* __restrict__ out,
       }
     }
   }
-  for (int i = tid; i < ENC_LUT_SIZE; i += kThreads) lut[i] = enc_lut_entry((uint32_t)i);
+  for (int i = tid; i < ENC_LUT_SIZE; i += kThreads) lut[i] = __ldg(g_enc_table.v + i);
   for (int w = 0; w < nwords; w++) stage[w * kThreads + tid] = 0u;  // coded bits are OR-ed in
   __syncthreads();  // the table is complete
   if (vz == 0) return;
@@ -246,7 +263,7 @@ __global__ void __launch_bounds__(128)
 zfp_encode_generic_kernel(FieldGeom g, const float* __restrict__ in, uint32_t* __restrict__ out, int maxbits,
                           uint64_t nblocks) {
   __shared__ uint32_t lut[ENC_LUT_SIZE];
-  for (int i = threadIdx.x; i < ENC_LUT_SIZE; i += blockDim.x) lut[i] = enc_lut_entry((uint32_t)i);
+  for (int i = threadIdx.x; i < ENC_LUT_SIZE; i += blockDim.x) lut[i] = __ldg(g_enc_table.v + i);
   __syncthreads();
   const uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= nblocks) return;
@@ -261,7 +278,7 @@ __global__ void __launch_bounds__(128)
 zfp_decode_generic_kernel(FieldGeom g, const uint32_t* __restrict__ in, float* __restrict__ out, int maxbits,
                           uint64_t nblocks, uint64_t total_words) {
   __shared__ uint32_t lut[DEC_LUT_SIZE];
-  for (int i = threadIdx.x; i < DEC_LUT_SIZE; i += blockDim.x) lut[i] = dec_lut_entry(i);
+  for (int i = threadIdx.x; i < DEC_LUT_SIZE; i += blockDim.x) lut[i] = __ldg(g_dec_table.v + i);
   __syncthreads();
   const uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= nblocks) return;
