@@ -80,3 +80,24 @@ def test_stream_sizes_agree(core, oracle):
         for maxbits in (37, 64, 300, 512):
             got = core.core_stream_bytes(C.c_size_t(dims[0]), C.c_size_t(dims[1]), C.c_size_t(dims[2]), maxbits)
             assert got == oracle.zfp_stream_bytes(*dims, maxbits)
+
+
+@pytest.mark.parametrize("maxbits", [32, 64, 128, 512, 1024])
+def test_decoders_agree_on_arbitrary_streams(core, oracle, maxbits):
+    """Decoding is defined for any bit string (a swapped-out tensor may come
+    back from a file): both decoders of the library's core must produce what
+    the oracle produces, bit for bit, also for streams no encoder wrote."""
+    nx, ny, nz = 32, 32, 8
+    nb = 8 * 8 * 2
+    words = nb * maxbits // 32
+    for sw in util.arbitrary_streams(words, maxbits):
+        s64 = np.zeros((words + 1) // 2, dtype=np.uint64)
+        s64.view(np.uint32)[:words] = sw
+        d = oracle.zfp_decode(s64, nx, ny, nz, maxbits)
+        inw = np.zeros(words + 4, dtype=np.uint32)
+        inw[:words] = sw
+        for fn in (core.core_decode, core.core_decode_pos):
+            out = np.zeros(nx * ny * nz, dtype=np.float32)
+            fn(inw.ctypes.data_as(C.c_void_p), C.c_size_t(nx), C.c_size_t(ny), C.c_size_t(nz), maxbits,
+               out.ctypes.data_as(C.c_void_p))
+            assert np.array_equal(d.view(np.uint32), out.view(np.uint32))

@@ -69,6 +69,24 @@ def both(env, a, dims, maxbits):
     assert torch.equal(back.view(torch.int32), cross.view(torch.int32))
 
 
+@pytest.mark.parametrize("maxbits", [64, 512, 1024])
+def test_decode_arbitrary_streams(env, maxbits):
+    """Streams no encoder wrote: the reference's decoder and the product's must
+    still agree on every bit (the reference's loops are bounded by the bit
+    budget whatever the content, decode.cuh:141-173)."""
+    import torch
+    cs, O, R = env
+    dims = (32, 32, 64)
+    n = 32 * 32 * 64
+    nbytes = O.zfp_stream_bytes(*dims, maxbits)
+    for sw in util.arbitrary_streams(nbytes // 4, maxbits):
+        padded = torch.zeros(nbytes + SLACK, dtype=torch.uint8, device="cuda")
+        padded[:nbytes] = torch.from_numpy(sw.view(np.uint8).copy()).cuda()
+        ref_back = ref_decompress(R, padded, dims, maxbits, n)
+        back = cs.zfp_decompress(padded[:nbytes].clone(), n, maxbits, dims)
+        assert torch.equal(back.view(torch.int32), ref_back.view(torch.int32))
+
+
 def test_config1(env):
     a = util.tanh_normal(128 * 64 * 32 * 32, seed=1)
     both(env, a, (32, 32, 8192), 512)

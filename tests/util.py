@@ -51,3 +51,18 @@ def block_zoo(n, seed=0):
         else:
             a[s] = np.sin(0.37 * np.arange(64) + b) * 1.5
     return a
+
+
+def arbitrary_streams(words, seed):
+    """uint32 streams that no encoder wrote: random bits, sparse bits, all
+    ones, and random bits behind 23 zero bits after every fourth word's header
+    (many empty leading planes)."""
+    rng = np.random.default_rng(seed)
+    dense = rng.integers(0, 2**32, words, dtype=np.uint64).astype(np.uint32)
+    sparse = dense & rng.integers(0, 2**32, words, dtype=np.uint64).astype(np.uint32) & \
+        rng.integers(0, 2**32, words, dtype=np.uint64).astype(np.uint32)
+    ones = np.full(words, 0xFFFFFFFF, dtype=np.uint32)
+    late = dense.copy()
+    late[0::4] &= np.uint32(0x1FF)
+    late[0::4] |= np.uint32(1)
+    return [dense, sparse | np.uint32(1), ones, late]
