@@ -268,6 +268,7 @@ class Execution {
   void reset_stats() { csw_mgr_reset_stats(mgr_); }
 
   int index = -1;
+  int lookahead = 1;          // swapped tensors whose return is started before backward asks for them
   long reclaimed = 0;         // tensors taken back before they had left the device
   long skipped_unsaved = 0;   // tensors nothing kept for backward: not copied out
   long dropped = 0;           // policy 1: let go without a copy
@@ -594,20 +595,23 @@ class Execution {
     }
     const int order = s.order;
     settle(s);
-    // One step ahead: start bringing back - copy AND decode, into a block taken now - the
-    // tensor swapped out just before this one, so that its consumer's backward finds it
-    // ready instead of waiting for a decode that starts only when it asks.
-    for (int i = order - 1; i >= 0; i--) {
+    // Ahead of need: start bringing back - copy AND decode, into blocks taken now - the
+    // `lookahead` tensors swapped out just before this one, so that their consumers'
+    // backward finds them ready instead of waiting for a decode that starts only when
+    // it asks.
+    int started = 0;
+    for (int i = order - 1; i >= 0 && started < lookahead; i--) {
       auto p = order_[i].lock();
       if (p && !p->restored && p->ticket) {
+        started++;
+        if (p->ahead.get() != nullptr) continue;  // already on its way
         int done = 1;
         // a lossless ticket still on its way out may yet be taken back whole
         if (p->policy != CSW_POLICY_ZFP) csw_swap_out_done(mgr_, p->ticket, &done);
-        if (done && p->ahead.get() == nullptr) {
+        if (done) {
           p->ahead = alloc->allocate(p->nbytes);
           check(csw_swap_in_start(mgr_, p->ticket, static_cast<float*>(p->ahead.get()), stream), "csw_swap_in_start");
         }
-        break;
       }
     }
     poll();

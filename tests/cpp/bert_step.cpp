@@ -179,7 +179,10 @@ static StepStats timed_steps(Bert& net, Execution& exe, const Batch& b, int step
   return r;
 }
 
+static int g_lookahead = 1;  // --lookahead: tensors whose return starts before backward asks
+
 static void init_exe(Execution& exe, const Dims& d, int nids, unsigned maxbits) {
+  exe.lookahead = g_lookahead;
   // pools sized for the model: about 1.5 GB of activations per layer at the BERT-base shape
   const size_t per_layer = (size_t)d.batch * d.seq * ((size_t)12 * d.hidden + 2 * d.ffn + 3 * (size_t)d.heads * d.seq) * 4;
   const size_t pinned = std::max<size_t>(size_t(1) << 30, per_layer * d.layers * 5 / 4);
@@ -350,6 +353,7 @@ int main(int argc, char** argv) {
     if (a == "--check") check = true;
     else if (a == "--bench") bench = true;
     else if (a == "--layers") { val(d.layers); layers_given = true; }
+    else if (a == "--lookahead") val(g_lookahead);
     else if (a == "--hidden") val(d.hidden);
     else if (a == "--heads") val(d.heads);
     else if (a == "--ffn") val(d.ffn);

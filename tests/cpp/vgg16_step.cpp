@@ -163,8 +163,11 @@ static StepStats timed_steps(Net& net, Execution& exe, const Batch& b, int steps
   return r;
 }
 
+static int g_lookahead = 1;  // --lookahead: tensors whose return starts before backward asks
+
 static void init_tables(Execution& exe, int pol) {
   exe.init_(64, 512, size_t(2) << 30, size_t(512) << 20);
+  exe.lookahead = g_lookahead;
   for (int i = 0; i < 50; i++) {
     exe.begin_stage[i] = i + 1;
     exe.policy[i] = pol;
@@ -542,6 +545,7 @@ int main(int argc, char** argv) {
     else if (a == "--warmup") val(warmup);
     else if (a == "--device") val(device);
     else if (a == "--seed") val(seed);
+    else if (a == "--lookahead") val(g_lookahead);
   }
   c10::cuda::set_device((c10::DeviceIndex)device);
   try {
