@@ -227,36 +227,48 @@ void destroy_ticket(csw_mgr* m, csw_ticket* t) {
 }
 
 // Non-blocking housekeeping: release staging whose last user has finished.
+// An event query costs more than a microsecond of host time, and this runs
+// inside every call, so it asks as few as the stream order allows.
 void poll(csw_mgr* m) {
+  // released tickets with work in flight, oldest first: stop at the first that is not
+  // finished (those behind it were released later and give their memory back a call or two
+  // later; a caller that needs memory now waits for the front, see pool_alloc)
   size_t z = 0;
-  for (size_t i = 0; i < m->zombies.size(); i++) {
-    csw_ticket* t = m->zombies[i];
-    if (event_done(t->ev_d2h) && event_done(t->ev_h2d) && event_done(t->ev_done)) destroy_ticket(m, t);
-    else m->zombies[z++] = t;
+  while (z < m->zombies.size()) {
+    csw_ticket* t = m->zombies[z];
+    if (!(event_done(t->ev_done) && event_done(t->ev_h2d) && event_done(t->ev_d2h))) break;
+    destroy_ticket(m, t);
+    z++;
   }
-  m->zombies.resize(z);
+  if (z) m->zombies.erase(m->zombies.begin(), m->zombies.begin() + z);
   size_t k = 0;
   // `live` is in submission order; raw copies go down one stream and compressed
   // payloads down another, so within a kind none has finished behind the first
-  // unfinished one
-  bool busy[2] = {false, false};
+  // unfinished one - on the way out and on the way back alike
+  bool out_busy[2] = {false, false}, in_busy[2] = {false, false};
   for (size_t i = 0; i < m->live.size(); i++) {
     csw_ticket* t = m->live[i];
+    const int kind = t->policy == CSW_POLICY_RAW ? 0 : 1;
     bool keep = true;
     if (t->state == T_OUT) {
-      bool& d2h_busy = busy[t->policy == CSW_POLICY_RAW ? 0 : 1];
-      if (!d2h_busy && cudaEventQuery(t->ev_d2h) == cudaSuccess) {
+      if (!out_busy[kind] && cudaEventQuery(t->ev_d2h) == cudaSuccess) {
         if (t->policy == CSW_POLICY_SPARSE) finalize_moved(m, t);
         free_stage(m, t);
         t->state = T_HOST;
         keep = false;
       } else {
-        d2h_busy = true;
+        out_busy[kind] = true;
       }
-    } else if (t->state == T_IN && t->ev_done && cudaEventQuery(t->ev_done) == cudaSuccess) {
-      free_stage(m, t);
-      t->state = T_HOST;
-      keep = false;
+    } else if (t->state == T_IN && t->ev_done) {
+      // the staged payload may still be on its way out when its decode has finished
+      if (!in_busy[kind] && cudaEventQuery(t->ev_done) == cudaSuccess && event_done(t->ev_d2h)) {
+        if (t->policy == CSW_POLICY_SPARSE && !t->moved_final) finalize_moved(m, t);
+        free_stage(m, t);
+        t->state = T_HOST;
+        keep = false;
+      } else {
+        in_busy[kind] = true;
+      }
     } else if (t->state == T_HOST || t->state == T_DEAD) {
       keep = false;
     }
@@ -265,6 +277,16 @@ void poll(csw_mgr* m) {
   }
   cudaGetLastError();  // cudaErrorNotReady from the queries is not an error
   m->live.resize(k);
+}
+
+void drop_from_live(csw_mgr* m, csw_ticket* t) {
+  if (!t->in_live) return;
+  for (size_t i = 0; i < m->live.size(); i++)
+    if (m->live[i] == t) {
+      m->live.erase(m->live.begin() + i);
+      break;
+    }
+  t->in_live = false;
 }
 
 // Pool allocation that first reclaims finished work and, if still short, waits
@@ -278,6 +300,7 @@ void* pool_alloc(csw_mgr* m, Pool& pool, size_t bytes, size_t* got) {
     csw_ticket* t = !m->zombies.empty() ? m->zombies.front() : m->live.front();
     cudaEvent_t ev = t->state == T_OUT ? t->ev_d2h : (t->ev_done ? t->ev_done : t->ev_d2h);
     if (ev) cudaEventSynchronize(ev);
+    if ((t->state == T_DEAD || t->state == T_IN) && t->ev_d2h) cudaEventSynchronize(t->ev_d2h);
     if (t->state == T_DEAD && t->ev_h2d) cudaEventSynchronize(t->ev_h2d);
     const size_t before = m->live.size() + m->zombies.size();
     poll(m);
@@ -540,7 +563,10 @@ static csw_status load_stage(csw_mgr* m, csw_ticket* t) {
         e = get_event(m, &t->ev_h2d);
         if (e != cudaSuccess) return cuda_fail(e);
       }
-      e = cudaEventRecord(t->ev_h2d, m->s_d2h_c);
+      // nothing to wait for but the codec that wrote it, which the decoder's own stream
+      // has behind it already; the copy out goes on reading the staged payload meanwhile
+      // (poll() keeps it until both have finished)
+      e = cudaEventRecord(t->ev_h2d, m->s_codec);
       return e == cudaSuccess ? CSW_OK : cuda_fail(e);
     }
   }
@@ -656,7 +682,8 @@ csw_status csw_ticket_release(csw_mgr* m, csw_ticket* t) {
   cudaGetLastError();
   if (idle && t->policy == CSW_POLICY_SPARSE && !t->moved_final) finalize_moved(m, t);
   t->state = T_DEAD;
-  poll(m);  // drops it from the live list
+  drop_from_live(m, t);
+  poll(m);
   if (idle) destroy_ticket(m, t);
   else m->zombies.push_back(t);
   return CSW_OK;

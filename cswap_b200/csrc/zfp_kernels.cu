@@ -293,6 +293,7 @@ zfp_decode_generic_kernel(FieldGeom g, const uint32_t* __restrict__ in, float* _
 // =====================================================================================
 // launchers
 // =====================================================================================
+constexpr size_t kDefaultDynamicSmem = 48 * 1024;  // what a kernel may ask for without opting in
 static size_t slab_smem_bytes(int maxbits, bool decode) {
   if (decode)
     return (size_t)((maxbits >> 5) + STAGE_SPARE_ROWS) * kThreads * 4 + DEC_LUT_SIZE * 4;
@@ -310,9 +311,11 @@ cudaError_t zfp_encode_launch(const FieldGeom& g, const float* in, void* out, in
   if (nblocks == 0) return cudaSuccess;
   if (zfp_slab_eligible(g, in, out, maxbits)) {
     const size_t smem = slab_smem_bytes(maxbits, false);
-    cudaError_t e = cudaFuncSetAttribute(zfp_encode_slab_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)slab_smem_bytes(2048, false));
-    if (e != cudaSuccess) return e;
+    if (smem > kDefaultDynamicSmem) {  // only the largest budgets: the call costs host time on every launch
+      cudaError_t e = cudaFuncSetAttribute(zfp_encode_slab_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)slab_smem_bytes(2048, false));
+      if (e != cudaSuccess) return e;
+    }
     const uint32_t ngroups = (g.nz + kGroupSlabs - 1) / kGroupSlabs;
     zfp_encode_slab_kernel<<<ngroups, kThreads, smem, stream>>>(in, reinterpret_cast<uint32_t*>(out), g.nz, maxbits,
                                                                pipe_consts());
@@ -341,9 +344,11 @@ cudaError_t zfp_decode_launch(const FieldGeom& g, const void* in, float* out, in
   if (nblocks == 0) return cudaSuccess;
   if (zfp_slab_eligible(g, out, in, maxbits)) {
     const size_t smem = slab_smem_bytes(maxbits, true);
-    cudaError_t e = cudaFuncSetAttribute(zfp_decode_slab_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)slab_smem_bytes(2048, true));
-    if (e != cudaSuccess) return e;
+    if (smem > kDefaultDynamicSmem) {
+      cudaError_t e = cudaFuncSetAttribute(zfp_decode_slab_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)slab_smem_bytes(2048, true));
+      if (e != cudaSuccess) return e;
+    }
     const uint32_t ngroups = (g.nz + kGroupSlabs - 1) / kGroupSlabs;
     zfp_decode_slab_kernel<<<ngroups, kThreads, smem, stream>>>(reinterpret_cast<const uint32_t*>(in), out, g.nz,
                                                                maxbits, pipe_consts());

@@ -654,16 +654,23 @@ class Execution {
   }
 
   // free device blocks whose swap-out has finished reading them (never blocks)
+  // An event query costs more than a microsecond of host time and this runs in every pre(),
+  // post() and restore: raw tensors are read by one of the manager's streams and compressed
+  // ones by another, each in the order the swaps were started, so within a kind nothing has
+  // finished behind the first entry that has not.
   void poll() {
     size_t k = 0;
+    bool busy[2] = {false, false};
     for (auto& s : reading_) {
       if (s->reading.get() == nullptr) continue;  // taken back: the storage owns the block again
-      int done = 1;
-      if (s->ticket) csw_swap_out_done(mgr_, s->ticket, &done);
+      const int kind = s->policy == CSW_POLICY_RAW ? 0 : 1;
+      int done = busy[kind] ? 0 : 1;
+      if (!busy[kind] && s->ticket) csw_swap_out_done(mgr_, s->ticket, &done);
       if (done) {
         s->reading.clear();
         if (s->restored) release_ticket(*s);
       } else {
+        busy[kind] = true;
         reading_[k++] = s;
       }
     }
