@@ -127,6 +127,7 @@ struct csw_ticket {
   size_t stage_cap = 0;
   bool stage_loaded = false;  // prefetch already brought the payload back
   bool in_live = false;       // listed in the manager's housekeeping list
+  bool cached = false;        // host copy complete, staged payload kept while the pool has room
   uint32_t* nnz_host = nullptr;  // slot in the manager's mapped count array
   int nnz_slot = -1;
   cudaEvent_t ev_read = nullptr;   // source tensor no longer read
@@ -139,9 +140,15 @@ struct csw_mgr {
   int device = 0;
   unsigned maxbits = 512;
   cudaStream_t s_codec = nullptr, s_d2h = nullptr, s_h2d = nullptr;
-  // copy out of compressed payloads: a stream of its own, so that a small payload does not
-  // queue behind the large raw copies already waiting for the link (both share it once running)
-  cudaStream_t s_d2h_c = nullptr;
+  // Raw tensors and compressed payloads leave through the ONE copy stream s_d2h.  Giving the
+  // payloads a stream of their own looked attractive (a small payload need not queue behind
+  // large raw copies) and measured badly: with two raw 48 MiB tensors among 119 compressed
+  // ones a BERT-shaped step took 288 ms instead of 236 - two outgoing copy streams at once
+  // slow the link down for both.  The copy engine serves device-to-host copies strictly in
+  // the order they were submitted, across streams and whatever their priorities or sizes
+  // (measured: a 4-byte read-back on another stream returns only when 4 GiB queued before it
+  // have left, 75 ms, also with the queue cut into 16 MiB pieces on a lowest-priority stream):
+  // a caller that reads a result back every step waits for the swap traffic queued so far.
   char* pinned_base = nullptr;
   char* staging_base = nullptr;
   Pool pinned, staging;
@@ -151,6 +158,7 @@ struct csw_mgr {
   std::vector<cudaEvent_t> free_events;
   std::vector<csw_ticket*> live;      // tickets whose staging may be reclaimable
   std::vector<csw_ticket*> zombies;   // released tickets whose copies are still in flight
+  std::vector<csw_ticket*> cache;     // tickets whose payload is on the host AND still staged, oldest first
   std::vector<csw_ticket*> all;       // every ticket not yet destroyed (so that destroy can free what callers kept)
   csw_mgr_stats stats{};
   std::mutex mu;
@@ -185,7 +193,18 @@ void put_event(csw_mgr* m, cudaEvent_t& ev) {
   ev = nullptr;
 }
 
+void uncache(csw_mgr* m, csw_ticket* t) {
+  if (!t->cached) return;
+  for (size_t i = 0; i < m->cache.size(); i++)
+    if (m->cache[i] == t) {
+      m->cache.erase(m->cache.begin() + i);
+      break;
+    }
+  t->cached = false;
+}
+
 void free_stage(csw_mgr* m, csw_ticket* t) {
+  uncache(m, t);
   if (t->stage) {
     m->staging.release(t->stage, t->stage_cap);
     t->stage = nullptr;
@@ -242,8 +261,8 @@ void poll(csw_mgr* m) {
   }
   if (z) m->zombies.erase(m->zombies.begin(), m->zombies.begin() + z);
   size_t k = 0;
-  // `live` is in submission order; raw copies go down one stream and compressed
-  // payloads down another, so within a kind none has finished behind the first
+  // `live` is in submission order; copies out go down one stream, raw copies in down a
+  // second and decodes down a third, so within a kind none has finished behind the first
   // unfinished one - on the way out and on the way back alike
   bool out_busy[2] = {false, false}, in_busy[2] = {false, false};
   for (size_t i = 0; i < m->live.size(); i++) {
@@ -253,7 +272,13 @@ void poll(csw_mgr* m) {
     if (t->state == T_OUT) {
       if (!out_busy[kind] && cudaEventQuery(t->ev_d2h) == cudaSuccess) {
         if (t->policy == CSW_POLICY_SPARSE) finalize_moved(m, t);
-        free_stage(m, t);
+        // The payload is on the host now.  Its staged copy stays where it is until the pool
+        // needs the room (pool_alloc evicts the oldest first): backward asks for the tensors
+        // swapped out last first, and those then come back without crossing the link again.
+        if (t->stage) {
+          t->cached = true;
+          m->cache.push_back(t);
+        }
         t->state = T_HOST;
         keep = false;
       } else {
@@ -296,6 +321,11 @@ void* pool_alloc(csw_mgr* m, Pool& pool, size_t bytes, size_t* got) {
   if (p) return p;
   poll(m);
   p = pool.alloc(bytes, got);
+  // staged payloads that are kept only because there was room: oldest out first
+  while (!p && &pool == &m->staging && !m->cache.empty()) {
+    free_stage(m, m->cache.front());
+    p = pool.alloc(bytes, got);
+  }
   while (!p && (!m->live.empty() || !m->zombies.empty())) {
     csw_ticket* t = !m->zombies.empty() ? m->zombies.front() : m->live.front();
     cudaEvent_t ev = t->state == T_OUT ? t->ev_d2h : (t->ev_done ? t->ev_done : t->ev_d2h);
@@ -305,6 +335,10 @@ void* pool_alloc(csw_mgr* m, Pool& pool, size_t bytes, size_t* got) {
     const size_t before = m->live.size() + m->zombies.size();
     poll(m);
     p = pool.alloc(bytes, got);
+    while (!p && &pool == &m->staging && !m->cache.empty()) {  // what the poll has just moved into the cache
+      free_stage(m, m->cache.front());
+      p = pool.alloc(bytes, got);
+    }
     if (!p && m->live.size() + m->zombies.size() == before) break;
   }
   return p;
@@ -341,7 +375,6 @@ csw_status csw_mgr_create(const csw_mgr_config* cfg, csw_mgr** out) {
   cudaDeviceGetStreamPriorityRange(&lo, &hi);
   if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&m->s_codec, cudaStreamNonBlocking, hi);
   if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&m->s_d2h, cudaStreamNonBlocking, hi);
-  if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&m->s_d2h_c, cudaStreamNonBlocking, hi);
   if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&m->s_h2d, cudaStreamNonBlocking, hi);
   if (e == cudaSuccess) e = cudaHostAlloc((void**)&m->pinned_base, pinned, cudaHostAllocPortable | cudaHostAllocMapped);
   if (e == cudaSuccess) e = cudaMalloc((void**)&m->staging_base, staging);
@@ -365,7 +398,6 @@ csw_status csw_mgr_destroy(csw_mgr* m) {
   DeviceGuard g(m->device);
   if (m->s_codec) cudaStreamSynchronize(m->s_codec);
   if (m->s_d2h) cudaStreamSynchronize(m->s_d2h);
-  if (m->s_d2h_c) cudaStreamSynchronize(m->s_d2h_c);
   if (m->s_h2d) cudaStreamSynchronize(m->s_h2d);
   // every ticket still alive, released or not: the streams are idle now, so all of it can go
   // (handles the caller still holds are invalid once the manager is gone)
@@ -375,7 +407,6 @@ csw_status csw_mgr_destroy(csw_mgr* m) {
   for (cudaEvent_t ev : m->free_events) cudaEventDestroy(ev);
   if (m->s_codec) cudaStreamDestroy(m->s_codec);
   if (m->s_d2h) cudaStreamDestroy(m->s_d2h);
-  if (m->s_d2h_c) cudaStreamDestroy(m->s_d2h_c);
   if (m->s_h2d) cudaStreamDestroy(m->s_h2d);
   if (m->pinned_base) cudaFreeHost(m->pinned_base);
   if (m->staging_base) cudaFree(m->staging_base);
@@ -432,7 +463,6 @@ csw_status csw_swap_out(csw_mgr* m, const float* d_ptr, size_t numel, int policy
     // before the memory it touches goes back to the pools
     cudaStreamSynchronize(m->s_codec);
     cudaStreamSynchronize(m->s_d2h);
-    cudaStreamSynchronize(m->s_d2h_c);
     cudaGetLastError();
     if (t->host) m->pinned.release(t->host, t->host_cap);
     free_stage(m, t);
@@ -476,9 +506,9 @@ csw_status csw_swap_out(csw_mgr* m, const float* d_ptr, size_t numel, int policy
                           cudaMemcpyDeviceToDevice, m->s_codec);
     if (st == CSW_OK && e == cudaSuccess) {
       e = cudaEventRecord(t->ev_read, m->s_codec);
-      if (e == cudaSuccess) e = cudaStreamWaitEvent(m->s_d2h_c, t->ev_read, 0);
-      if (e == cudaSuccess) e = cudaMemcpyAsync(t->host, t->stage, zbytes, cudaMemcpyDeviceToHost, m->s_d2h_c);
-      if (e == cudaSuccess) e = cudaEventRecord(t->ev_d2h, m->s_d2h_c);
+      if (e == cudaSuccess) e = cudaStreamWaitEvent(m->s_d2h, t->ev_read, 0);
+      if (e == cudaSuccess) e = cudaMemcpyAsync(t->host, t->stage, zbytes, cudaMemcpyDeviceToHost, m->s_d2h);
+      if (e == cudaSuccess) e = cudaEventRecord(t->ev_d2h, m->s_d2h);
     }
     t->moved = zbytes;
     t->moved_final = true;
@@ -490,14 +520,14 @@ csw_status csw_swap_out(csw_mgr* m, const float* d_ptr, size_t numel, int policy
     st = csw_sparse_compress_onepass(d_ptr, numel, t->stage, t->stage_cap, nnz_dev, m->s_codec);
     if (st == CSW_OK) {
       e = cudaEventRecord(t->ev_read, m->s_codec);
-      if (e == cudaSuccess) e = cudaStreamWaitEvent(m->s_d2h_c, t->ev_read, 0);
+      if (e == cudaSuccess) e = cudaStreamWaitEvent(m->s_d2h, t->ev_read, 0);
       if (e == cudaSuccess) {
-        sparse_to_host_kernel<<<32, 256, 0, m->s_d2h_c>>>(reinterpret_cast<const uint4*>(t->stage),
+        sparse_to_host_kernel<<<32, 256, 0, m->s_d2h>>>(reinterpret_cast<const uint4*>(t->stage),
                                                         reinterpret_cast<uint4*>(t->host), nnz_dev, t->nnz_host,
                                                         L.values);
         e = cudaGetLastError();
       }
-      if (e == cudaSuccess) e = cudaEventRecord(t->ev_d2h, m->s_d2h_c);
+      if (e == cudaSuccess) e = cudaEventRecord(t->ev_d2h, m->s_d2h);
     }
     t->moved = L.bound;  // upper bound until the count lands
   }
@@ -570,6 +600,17 @@ static csw_status load_stage(csw_mgr* m, csw_ticket* t) {
       return e == cudaSuccess ? CSW_OK : cuda_fail(e);
     }
   }
+  if (t->stage && t->cached) {
+    // on the host and still staged: nothing crosses the link
+    uncache(m, t);
+    t->stage_loaded = true;
+    if (!t->ev_h2d) {
+      e = get_event(m, &t->ev_h2d);
+      if (e != cudaSuccess) return cuda_fail(e);
+    }
+    e = cudaEventRecord(t->ev_h2d, m->s_codec);
+    return e == cudaSuccess ? CSW_OK : cuda_fail(e);
+  }
   if (!t->moved_final) {
     e = cudaEventSynchronize(t->ev_d2h);
     if (e != cudaSuccess) return cuda_fail(e);
@@ -588,6 +629,7 @@ static csw_status load_stage(csw_mgr* m, csw_ticket* t) {
   if (e == cudaSuccess) e = cudaEventRecord(t->ev_h2d, m->s_h2d);
   if (e != cudaSuccess) return cuda_fail(e);
   t->stage_loaded = true;
+  m->stats.moved_bytes_in += t->moved;
   return CSW_OK;
 }
 
@@ -667,7 +709,7 @@ csw_status csw_swap_in_start(csw_mgr* m, csw_ticket* t, float* d_dst, csw_stream
   }
   m->stats.swap_ins++;
   m->stats.raw_bytes_in += raw;
-  m->stats.moved_bytes_in += t->moved;
+  if (t->policy == CSW_POLICY_RAW) m->stats.moved_bytes_in += raw;  // codec tickets count in load_stage, when they cross
   return CSW_OK;
 }
 
@@ -840,10 +882,11 @@ csw_status csw_mgr_sync(csw_mgr* m) {
   DeviceGuard g(m->device);
   cudaError_t e = cudaStreamSynchronize(m->s_codec);
   if (e == cudaSuccess) e = cudaStreamSynchronize(m->s_d2h);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(m->s_d2h_c);
   if (e == cudaSuccess) e = cudaStreamSynchronize(m->s_h2d);
   if (e != cudaSuccess) return cuda_fail(e);
   poll(m);
+  // "everything is on the host": the staged copies kept for a quick return go as well
+  while (!m->cache.empty()) free_stage(m, m->cache.front());
   return CSW_OK;
 }
 

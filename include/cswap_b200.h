@@ -183,7 +183,10 @@ typedef struct csw_ticket csw_ticket; /* one swapped-out tensor        */
 typedef struct {
   int device;               /* CUDA device ordinal                                   */
   size_t pinned_bytes;      /* pinned host pool (0: 1 GiB)                           */
-  size_t staging_bytes;     /* device pool for compressed staging (0: 512 MiB)       */
+  size_t staging_bytes;     /* device pool for compressed staging (0: 512 MiB); a
+                               payload stays staged after its copy out until the
+                               pool needs the room, and a swap-in that still finds
+                               it there does not cross the link                      */
   unsigned zfp_maxbits;     /* bits per block for CSW_POLICY_ZFP (0: 512 = rate 8);
                                the reference's setRatio(), CSWAP+/Execution.h:63     */
 } csw_mgr_config;
@@ -277,12 +280,14 @@ csw_status csw_blob_import(csw_mgr* m, const void* blob, size_t bytes, csw_ticke
 typedef struct {
   uint64_t swap_outs, swap_ins;
   uint64_t raw_bytes_out, moved_bytes_out; /* uncompressed vs. on-link, swap-out */
-  uint64_t raw_bytes_in, moved_bytes_in;
+  uint64_t raw_bytes_in, moved_bytes_in;   /* moved: what really crossed the link coming back */
   size_t pinned_in_use, pinned_high_water, staging_in_use, staging_high_water;
 } csw_mgr_stats;
 csw_status csw_mgr_get_stats(csw_mgr* m, csw_mgr_stats* s);
 csw_status csw_mgr_reset_stats(csw_mgr* m);
-/* Block the host until every queued swap-out and swap-in has finished. */
+/* Block the host until every queued swap-out and swap-in has finished; staged
+   payloads kept for a quick return are dropped (afterwards every tensor swapped
+   out is on the host only). */
 csw_status csw_mgr_sync(csw_mgr* m);
 
 /* ---- 5. cost model --------------------------------------------------------- */
