@@ -159,6 +159,7 @@ struct csw_mgr {
   std::vector<csw_ticket*> live;      // tickets whose staging may be reclaimable
   std::vector<csw_ticket*> zombies;   // released tickets whose copies are still in flight
   std::vector<csw_ticket*> cache;     // tickets whose payload is on the host AND still staged, oldest first
+  bool keep_staged = true;
   std::vector<csw_ticket*> all;       // every ticket not yet destroyed (so that destroy can free what callers kept)
   csw_mgr_stats stats{};
   std::mutex mu;
@@ -275,9 +276,11 @@ void poll(csw_mgr* m) {
         // The payload is on the host now.  Its staged copy stays where it is until the pool
         // needs the room (pool_alloc evicts the oldest first): backward asks for the tensors
         // swapped out last first, and those then come back without crossing the link again.
-        if (t->stage) {
+        if (t->stage && m->keep_staged) {
           t->cached = true;
           m->cache.push_back(t);
+        } else {
+          free_stage(m, t);
         }
         t->state = T_HOST;
         keep = false;
@@ -422,6 +425,15 @@ csw_status csw_mgr_set_zfp_maxbits(csw_mgr* m, unsigned maxbits) {
   if (csw_zfp_max_bytes(32, 32, 4, maxbits, &b) != CSW_OK) return CSW_ERR_ARG;
   std::lock_guard<std::mutex> lk(m->mu);
   m->maxbits = maxbits;
+  return CSW_OK;
+}
+
+csw_status csw_mgr_keep_staged(csw_mgr* m, int keep) {
+  if (!m) return CSW_ERR_ARG;
+  std::lock_guard<std::mutex> lk(m->mu);
+  m->keep_staged = keep != 0;
+  if (!m->keep_staged)
+    while (!m->cache.empty()) free_stage(m, m->cache.front());
   return CSW_OK;
 }
 

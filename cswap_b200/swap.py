@@ -189,6 +189,11 @@ class SwapManager:
         check(lib().csw_mgr_set_zfp_maxbits(self._h, maxbits), "csw_mgr_set_zfp_maxbits")
         self.zfp_maxbits = maxbits
 
+    def keep_staged(self, keep: bool) -> None:
+        """Whether a compressed payload stays in device staging after its copy
+        out, until the pool needs the room (default), or is released at once."""
+        check(lib().csw_mgr_keep_staged(self._h, 1 if keep else 0), "csw_mgr_keep_staged")
+
     def swap_out(self, t: torch.Tensor, policy: int) -> Ticket:
         _require_cuda_f32(t, "t")
         h = C.c_void_p()

@@ -194,6 +194,10 @@ typedef struct {
 csw_status csw_mgr_create(const csw_mgr_config* cfg, csw_mgr** out);
 csw_status csw_mgr_destroy(csw_mgr* m);
 csw_status csw_mgr_set_zfp_maxbits(csw_mgr* m, unsigned maxbits);
+/* keep = 0: a staged payload is released as soon as its copy out has finished, so every
+ * swap-in of it crosses the link; keep != 0 (the default): it stays until the staging pool
+ * needs the room. */
+csw_status csw_mgr_keep_staged(csw_mgr* m, int keep);
 /* The manager's own streams (the reference's stream1, CSWAP+/Execution.h:49,
  * split by role), e.g. to tell a caching allocator that a tensor handed to
  * csw_swap_out is still being read on them. */

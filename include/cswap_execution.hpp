@@ -99,6 +99,8 @@ class Execution {
     }
     maxbits_ = zfp_maxbits;
   }
+  // See csw_mgr_keep_staged: compressed payloads kept on the device while the staging pool has room.
+  void keep_staged(bool keep) { check(csw_mgr_keep_staged(mgr_, keep ? 1 : 0), "csw_mgr_keep_staged"); }
   void setRatio(unsigned maxbits) {
     check(csw_mgr_set_zfp_maxbits(mgr_, maxbits), "csw_mgr_set_zfp_maxbits");
     maxbits_ = maxbits;

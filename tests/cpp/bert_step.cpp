@@ -322,6 +322,10 @@ static int run_bench(Dims d, int steps, int warmup, int seed) {
   o << ", \"raw_swap\": " << row_json(timed_steps(net, exe, b, steps, warmup));
   fill(exe, last_use, CSW_POLICY_ZFP);
   o << ", \"zfp16_everywhere\": " << row_json(timed_steps(net, exe, b, steps, warmup));
+  // the same with every staged payload released once it is on the host: all of it comes back over the link
+  exe.keep_staged(false);
+  o << ", \"zfp16_everywhere_nothing_kept_staged\": " << row_json(timed_steps(net, exe, b, steps, warmup));
+  exe.keep_staged(true);
   // self-tuned: loss allowed on every float activation
   std::set<int> lossy;
   for (auto& kv : prof)

@@ -453,6 +453,13 @@ static int run_bench(int batch, int steps, int warmup, int seed) {
     init_tables(exe, CSW_POLICY_ZFP);
     o << ", \"zfp8_everywhere\": " << row_json(timed_steps(net, exe, b, steps, warmup));
   }
+  {
+    // the same with every staged payload released once it is on the host: all of it comes back over the link
+    Execution exe;
+    init_tables(exe, CSW_POLICY_ZFP);
+    exe.keep_staged(false);
+    o << ", \"zfp8_everywhere_nothing_kept_staged\": " << row_json(timed_steps(net, exe, b, steps, warmup));
+  }
   for (int planner : {3, 4}) {
     Execution exe;
     init_tables(exe, CSW_POLICY_KEEP);

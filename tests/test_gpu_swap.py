@@ -478,3 +478,72 @@ def test_profile_and_make_policy(cs):
     cap_slow = exe.make_policy_capuchin(prof, slow, min_bytes=1 << 16)
     assert cap_slow.count(1) > cap.count(1) and cap_slow.count(1) >= 2
     exe.mgr.close()
+
+
+def test_staged_payload_kept_until_the_pool_needs_room(cs):
+    """A compressed payload stays in device staging after its copy out: a
+    swap-in that finds it there moves nothing over the link; with the pool too
+    small for all of them the oldest make room (and come back over the link);
+    csw_mgr_keep_staged(0) or csw_mgr_sync drop the kept copies.  The tensors
+    that come back are the same bits in every case."""
+    import time
+    import torch
+
+    def settle(m, tickets):
+        # wait (without csw_mgr_sync, which drops the kept copies) until the copies out are done
+        torch.cuda.synchronize()
+        for _ in range(2000):
+            if all(m.out_done(tk) for tk in tickets):
+                break
+            time.sleep(0.001)
+        time.sleep(0.05)  # the copies out (4 MiB each) trail the codec; no call waits for them without dropping the kept copies
+        m.stats()         # a call that runs the manager's housekeeping
+
+    ts = [torch.from_numpy(util.tanh_normal(4 << 20, seed=i)).cuda() for i in range(4)]  # 16 MiB each, 4 MiB coded
+    want = []
+    ref = cs.SwapManager(pinned_bytes=256 << 20, staging_bytes=64 << 20)
+    ref.keep_staged(False)
+    for t in ts:
+        tk = ref.swap_out(t, cs.POLICY_ZFP)
+        settle(ref, [tk])
+        want.append(ref.swap_in(tk).clone())
+        tk.release()
+    torch.cuda.synchronize()
+    s = ref.stats()
+    assert s["moved_bytes_in"] == s["moved_bytes_out"] == 4 * (4 << 20)  # released at once: all of it crossed again
+    ref.close()
+
+    m = cs.SwapManager(pinned_bytes=256 << 20, staging_bytes=64 << 20)
+    tks = [m.swap_out(t, cs.POLICY_ZFP) for t in ts]
+    settle(m, tks)
+    for tk, w in zip(reversed(tks), reversed(want)):
+        assert torch.equal(m.swap_in(tk), w)
+    torch.cuda.synchronize()
+    assert m.stats()["moved_bytes_in"] == 0           # all four were still staged
+    for tk in tks:
+        tk.release()
+    m.close()
+
+    small = cs.SwapManager(pinned_bytes=256 << 20, staging_bytes=10 << 20)  # room for two payloads
+    tks = []
+    for t in ts:
+        tks.append(small.swap_out(t, cs.POLICY_ZFP))
+        settle(small, tks)
+    for tk, w in zip(reversed(tks), reversed(want)):
+        assert torch.equal(small.swap_in(tk), w)
+    torch.cuda.synchronize()
+    got = small.stats()["moved_bytes_in"]
+    assert 0 < got < 4 * (4 << 20)                    # the newest were kept, the oldest had to make room
+    for tk in tks:
+        tk.release()
+    small.close()
+
+    m = cs.SwapManager(pinned_bytes=256 << 20, staging_bytes=64 << 20)
+    tk = m.swap_out(ts[0], cs.POLICY_ZFP)
+    m.sync()                                          # everything on the host only
+    assert m.stats()["staging_in_use"] == 0
+    assert torch.equal(m.swap_in(tk), want[0])
+    torch.cuda.synchronize()
+    assert m.stats()["moved_bytes_in"] == 4 << 20
+    tk.release()
+    m.close()
