@@ -601,6 +601,7 @@ def vgg16_block(args, cs, torch, dev, world, rank):
     t0 = rows["no_swap"]["ms_median"]
     eps_list = (0.1, 0.25, 0.5, 1.0)
     lossless = {tid: (cs.POLICY_SPARSE if p["zero_fraction"] >= 0.3 else cs.POLICY_RAW) for tid, p in prof.items()}
+    mgr.keep_staged(False)  # strict for the sweeps: whatever comes back crosses the link again
     sweeps = {
         "raw": hidden_bytes_sweep(W, cs, torch, model, mgr, make_batch, prof, lambda tid: cs.POLICY_RAW, t0, eps_list),
         # the reference's rule for where loss is allowed: ZFP-8 on conv inputs, lossless elsewhere
