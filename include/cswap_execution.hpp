@@ -270,6 +270,7 @@ class Execution {
   void reset_stats() { csw_mgr_reset_stats(mgr_); }
 
   int index = -1;
+  bool free_after_codec = true;  // compressed policies: the compute stream waits for the codec's read, the block is freed at once
   int lookahead = 1;          // swapped tensors whose return is started before backward asks for them
   long reclaimed = 0;         // tensors taken back before they had left the device
   long skipped_unsaved = 0;   // tensors nothing kept for backward: not copied out
@@ -557,8 +558,18 @@ class Execution {
       // detach the device block from the storage; a swapped block is freed once the
       // manager's streams are done with it, a dropped one at once
       s->reading = s->storage->set_data_ptr(at::DataPtr(nullptr, s->storage->device()));
-      if (s->policy == CSW_POLICY_DROP) s->reading.clear();
-      else reading_.push_back(s);
+      if (s->policy == CSW_POLICY_DROP) {
+        s->reading.clear();
+      } else if (free_after_codec && (s->policy == CSW_POLICY_ZFP || s->policy == CSW_POLICY_SPARSE)) {
+        // the codec reads the tensor in a fraction of the time the link needs for it: let the
+        // compute stream wait for that read and give the block back at once, as a free in
+        // stream order - the memory is reusable by the very next layer however far the host
+        // runs ahead of the GPU, instead of whenever a poll finds the read finished
+        check(csw_swap_out_wait(mgr_, s->ticket, c10::cuda::getCurrentCUDAStream().stream()), "csw_swap_out_wait");
+        s->reading.clear();
+      } else {
+        reading_.push_back(s);
+      }
       fn->add_pre_hook(std::make_unique<RestoreHook>(s));
     }
     pending_.clear();
