@@ -111,6 +111,9 @@ class SwapManager:
         # with them, never waited for.
         self._retiring: list = []
         self.reclaimed_tensors = 0
+        # compressed policies: make the caller's stream wait for the codec's read instead
+        # of holding the source tensor until a poll finds the read finished
+        self.free_after_codec = True
 
     def close(self) -> None:
         if self._h is not None:
@@ -201,7 +204,13 @@ class SwapManager:
               "csw_swap_out")
         tk = Ticket(self, h.value, t.shape, t.numel(), t.device, policy)
         self._poll()
-        self._reading.append((tk, t))
+        if self.free_after_codec and policy in (POLICY_ZFP, POLICY_SPARSE):
+            # the codec reads the tensor in a fraction of the time the link needs for it:
+            # the caller's stream waits for that read, after which the block may be reused
+            # in stream order - no reference is kept, however far the host runs ahead
+            self.out_wait(tk)
+        else:
+            self._reading.append((tk, t))
         return tk
 
     def import_blob(self, blob, shape=None) -> Ticket:
