@@ -346,6 +346,33 @@ static int run_check(int batch) {
       if (r.loss != base.loss || s.swap_outs != 1 || d_exact == 0.0 || d_lossy > 1e-3 * d_exact) bad++;
     }
   }
+  {
+    // The engine's knobs change WHEN things move, never what comes back: ZFP-8 on every kept
+    // activation gives the same loss and gradients, bit for bit, whether blocks are freed in
+    // stream order or by polling, however many tensors are brought back ahead of need, and
+    // whether staged payloads are kept on the device or come back over the link.
+    Result z0;
+    {
+      Execution exe;
+      init_tables(exe, CSW_POLICY_ZFP);
+      z0 = one_step(net, exe, b);
+    }
+    struct Knobs { const char* name; bool free_after_codec; int lookahead; bool keep_staged; };
+    for (const Knobs k : {Knobs{"blocks freed by polling", false, 1, true}, Knobs{"three tensors ahead", true, 3, true},
+                          Knobs{"nothing kept staged", true, 1, false}, Knobs{"nothing ahead", false, 0, false}}) {
+      Execution exe;
+      init_tables(exe, CSW_POLICY_ZFP);
+      exe.free_after_codec = k.free_after_codec;
+      exe.lookahead = k.lookahead;
+      exe.keep_staged(k.keep_staged);
+      Result r = one_step(net, exe, b);
+      const csw_mgr_stats s = exe.stats();
+      const bool ok = same(r, z0) && s.swap_outs >= 10 && s.swap_ins == s.swap_outs;
+      std::printf("ZFP-8 everywhere, %-24s swap_outs %3llu link bytes in %9llu identical to the default engine %d\n", k.name,
+                  (unsigned long long)s.swap_outs, (unsigned long long)s.moved_bytes_in, (int)same(r, z0));
+      if (!ok) bad++;
+    }
+  }
   std::printf(bad ? "FAIL\n" : "PASS\n");
   return bad ? 1 : 0;
 }

@@ -23,15 +23,18 @@ def test_cpp_vgg16_step_policies():
     """VGG16 at batch 128 under the C++ Execution (tests/cpp/vgg16_step.cpp --check):
     policies 1 / 2 / 3, the vDNN and SuperNeurons planners and the self-tuned
     lossless table are bit-identical to the step without swapping, the profile
-    knows which activations nothing keeps, and policy 6 hands backward exactly
-    decode(encode(x))."""
+    knows which activations nothing keeps, policy 6 hands backward exactly
+    decode(encode(x)), and the engine's knobs (stream-ordered freeing, how far
+    ahead tensors are brought back, staged payloads kept or not) leave the ZFP
+    step's loss and gradients bit-identical."""
     from cswap_b200 import build
     exe = build.build_cpp_driver(name="vgg16_step")
     r = subprocess.run([exe, "--check"], capture_output=True, text=True, timeout=600)
     print(r.stdout, r.stderr[-2000:])
     assert r.returncode == 0 and "PASS" in r.stdout
     for tag in ("policy 2 (raw)", "policy 3 (sparse)", "policy 1 (drop)", "policy_ 3 (vDNN)", "policy_ 4 (SuperNeurons)",
-                "self-tuned (lossless)", "policy 6 on id 2", "policy 6 on id 6"):
+                "self-tuned (lossless)", "policy 6 on id 2", "policy 6 on id 6", "blocks freed by polling",
+                "three tensors ahead", "nothing kept staged", "nothing ahead"):
         assert tag in r.stdout
 
 
