@@ -20,8 +20,15 @@
 //  * swap-out and swap-in go through csw_swap_out / csw_swap_in: events between
 //    streams, pooled pinned memory, no stream synchronisation, no blocking read
 //    of the sparse count (Execution.h:77,92,236);
-//  * a tensor's device block is handed back to the caching allocator only once
-//    the manager's streams have finished reading it (polled, never waited for);
+//  * a tensor's device block goes back to the caching allocator as soon as it is
+//    safe: under the compressed policies the compute stream waits for the codec's
+//    read of it (tens of microseconds) and the block is freed at once, in stream
+//    order, so the next layer reuses it however far the host runs ahead of the
+//    GPU; under raw swap, whose read is the copy itself, the block is freed when
+//    a poll finds the copy finished (never waited for);
+//  * tensors come back one step ahead of need (copy and decode started when the
+//    tensor swapped out after them is restored), from the payload still staged
+//    on the device where the manager has kept it;
 //  * a tensor that nothing holds for backward once its consumer has run is not
 //    copied out at all, and a losslessly swapped tensor that backward asks for
 //    before its copy out has finished is handed back as it is;
