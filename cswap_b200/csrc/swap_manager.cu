@@ -128,6 +128,9 @@ struct csw_ticket {
   bool stage_loaded = false;  // prefetch already brought the payload back
   bool in_live = false;       // listed in the manager's housekeeping list
   bool cached = false;        // host copy complete, staged payload kept while the pool has room
+  bool queued = false;        // raw: the copy out has not been handed to the copy stream yet
+  const float* src = nullptr; // raw: the tensor to copy while queued
+  cudaEvent_t ev_ready = nullptr;  // raw, while queued: the producer's work on the caller's stream
   uint32_t* nnz_host = nullptr;  // slot in the manager's mapped count array
   int nnz_slot = -1;
   cudaEvent_t ev_read = nullptr;   // source tensor no longer read
@@ -160,6 +163,10 @@ struct csw_mgr {
   std::vector<csw_ticket*> zombies;   // released tickets whose copies are still in flight
   std::vector<csw_ticket*> cache;     // tickets whose payload is on the host AND still staged, oldest first
   bool keep_staged = true;
+  // Raw copies out are handed to the copy stream a few at a time (see submit_raw): the rest
+  // wait here, in order, and a ticket released while it waits is never copied at all.
+  std::vector<csw_ticket*> raw_queue;
+  std::vector<csw_ticket*> raw_flying;  // handed over, copy not yet known to be finished
   std::vector<csw_ticket*> all;       // every ticket not yet destroyed (so that destroy can free what callers kept)
   csw_mgr_stats stats{};
   std::mutex mu;
@@ -229,7 +236,11 @@ void finalize_moved(csw_mgr* m, csw_ticket* t) {
 bool event_done(cudaEvent_t ev) { return !ev || cudaEventQuery(ev) == cudaSuccess; }
 
 // Return everything a released ticket holds to the pools and free it.
+void forget_raw(csw_mgr* m, csw_ticket* t);
+void pump_raw(csw_mgr* m);
+void submit_raw_through(csw_mgr* m, csw_ticket* t);
 void destroy_ticket(csw_mgr* m, csw_ticket* t) {
+  forget_raw(m, t);
   free_stage(m, t);
   if (t->host) m->pinned.release(t->host, t->host_cap);
   if (t->nnz_slot >= 0) m->free_slots.push_back(t->nnz_slot);
@@ -271,7 +282,7 @@ void poll(csw_mgr* m) {
     const int kind = t->policy == CSW_POLICY_RAW ? 0 : 1;
     bool keep = true;
     if (t->state == T_OUT) {
-      if (!out_busy[kind] && cudaEventQuery(t->ev_d2h) == cudaSuccess) {
+      if (!out_busy[kind] && !t->queued && cudaEventQuery(t->ev_d2h) == cudaSuccess) {
         if (t->policy == CSW_POLICY_SPARSE) finalize_moved(m, t);
         // The payload is on the host now.  Its staged copy stays where it is until the pool
         // needs the room (pool_alloc evicts the oldest first): backward asks for the tensors
@@ -305,6 +316,7 @@ void poll(csw_mgr* m) {
   }
   cudaGetLastError();  // cudaErrorNotReady from the queries is not an error
   m->live.resize(k);
+  pump_raw(m);
 }
 
 void drop_from_live(csw_mgr* m, csw_ticket* t) {
@@ -315,6 +327,70 @@ void drop_from_live(csw_mgr* m, csw_ticket* t) {
       break;
     }
   t->in_live = false;
+}
+
+// ---- raw copies out, a few at a time ------------------------------------------------
+// The copy engine serves device-to-host copies strictly in the order they were
+// submitted, so whatever is queued on it stands between the caller and its next
+// read-back; and a raw tensor that backward wants before its copy has run is
+// handed back as it is, which makes that copy wasted link time.  So at most
+// kRawInFlight raw copies are on the copy stream at a time; the others wait in
+// raw_queue and are submitted as those finish (every call pumps), or when a call
+// needs one of them to have happened.
+constexpr size_t kRawInFlight = 2;
+
+cudaError_t submit_raw(csw_mgr* m, csw_ticket* t) {
+  cudaError_t e = cudaStreamWaitEvent(m->s_d2h, t->ev_ready, 0);
+  if (e == cudaSuccess)
+    e = cudaMemcpyAsync(t->host, t->src, t->numel * sizeof(float), cudaMemcpyDeviceToHost, m->s_d2h);
+  if (e == cudaSuccess) e = cudaEventRecord(t->ev_read, m->s_d2h);
+  if (e == cudaSuccess) e = cudaEventRecord(t->ev_d2h, m->s_d2h);
+  put_event(m, t->ev_ready);
+  t->queued = false;
+  t->src = nullptr;
+  m->stats.moved_bytes_out += t->moved;
+  m->raw_flying.push_back(t);
+  return e;
+}
+
+void pump_raw(csw_mgr* m) {
+  size_t done = 0;  // in order on one stream: nothing has finished behind the first that has not
+  while (done < m->raw_flying.size() && cudaEventQuery(m->raw_flying[done]->ev_d2h) == cudaSuccess) done++;
+  if (done) m->raw_flying.erase(m->raw_flying.begin(), m->raw_flying.begin() + done);
+  cudaGetLastError();
+  size_t n = 0;
+  while (n < m->raw_queue.size() && m->raw_flying.size() < kRawInFlight) submit_raw(m, m->raw_queue[n++]);
+  if (n) m->raw_queue.erase(m->raw_queue.begin(), m->raw_queue.begin() + n);
+}
+
+// A call needs this ticket's copy to have been issued: issue it and everything queued before it.
+void submit_raw_through(csw_mgr* m, csw_ticket* t) {
+  if (!t->queued) return;
+  size_t n = 0;
+  while (n < m->raw_queue.size()) {
+    csw_ticket* q = m->raw_queue[n++];
+    submit_raw(m, q);
+    if (q == t) break;
+  }
+  m->raw_queue.erase(m->raw_queue.begin(), m->raw_queue.begin() + n);
+}
+
+void forget_raw(csw_mgr* m, csw_ticket* t) {  // the ticket is going away
+  for (size_t i = 0; i < m->raw_queue.size(); i++)
+    if (m->raw_queue[i] == t) {
+      m->raw_queue.erase(m->raw_queue.begin() + i);
+      break;
+    }
+  for (size_t i = 0; i < m->raw_flying.size(); i++)
+    if (m->raw_flying[i] == t) {
+      m->raw_flying.erase(m->raw_flying.begin() + i);
+      break;
+    }
+  if (t->queued) {
+    put_event(m, t->ev_ready);
+    t->queued = false;
+    t->src = nullptr;
+  }
 }
 
 // Pool allocation that first reclaims finished work and, if still short, waits
@@ -331,6 +407,7 @@ void* pool_alloc(csw_mgr* m, Pool& pool, size_t bytes, size_t* got) {
   }
   while (!p && (!m->live.empty() || !m->zombies.empty())) {
     csw_ticket* t = !m->zombies.empty() ? m->zombies.front() : m->live.front();
+    submit_raw_through(m, t);
     cudaEvent_t ev = t->state == T_OUT ? t->ev_d2h : (t->ev_done ? t->ev_done : t->ev_d2h);
     if (ev) cudaEventSynchronize(ev);
     if ((t->state == T_DEAD || t->state == T_IN) && t->ev_d2h) cudaEventSynchronize(t->ev_d2h);
@@ -499,18 +576,20 @@ csw_status csw_swap_out(csw_mgr* m, const float* d_ptr, size_t numel, int policy
   cudaEvent_t ev_ready = nullptr;
   e = get_event(m, &ev_ready);
   if (e == cudaSuccess) e = cudaEventRecord(ev_ready, compute);
-  cudaStream_t first = policy == CSW_POLICY_RAW ? m->s_d2h : m->s_codec;
-  if (e == cudaSuccess) e = cudaStreamWaitEvent(first, ev_ready, 0);
-  put_event(m, ev_ready);
+  if (e == cudaSuccess && policy != CSW_POLICY_RAW) e = cudaStreamWaitEvent(m->s_codec, ev_ready, 0);
+  if (policy != CSW_POLICY_RAW || e != cudaSuccess) put_event(m, ev_ready);
   if (e != cudaSuccess) return fail(cuda_fail(e));
 
   csw_status st = CSW_OK;
   if (policy == CSW_POLICY_RAW) {
-    e = cudaMemcpyAsync(t->host, d_ptr, raw, cudaMemcpyDeviceToHost, m->s_d2h);
-    if (e == cudaSuccess) e = cudaEventRecord(t->ev_read, m->s_d2h);
-    if (e == cudaSuccess) e = cudaEventRecord(t->ev_d2h, m->s_d2h);
+    // queued; pump_raw hands it to the copy stream when fewer than kRawInFlight are on it
+    t->ev_ready = ev_ready;
+    t->src = d_ptr;
+    t->queued = true;
     t->moved = raw;
     t->moved_final = true;
+    m->raw_queue.push_back(t);
+    pump_raw(m);
   } else if (policy == CSW_POLICY_ZFP) {
     st = csw_zfp_compress(d_ptr, 32, 32, nz, m->maxbits, t->stage, t->stage_cap, nullptr, m->s_codec);
     if (st == CSW_OK && zbytes > zstream)  // the values past the last whole slab
@@ -548,7 +627,7 @@ csw_status csw_swap_out(csw_mgr* m, const float* d_ptr, size_t numel, int policy
 
   m->stats.swap_outs++;
   m->stats.raw_bytes_out += raw;
-  if (t->moved_final) m->stats.moved_bytes_out += t->moved;
+  if (t->moved_final && policy != CSW_POLICY_RAW) m->stats.moved_bytes_out += t->moved;  // raw: when its copy is issued
   m->live.push_back(t);
   t->in_live = true;
   m->all.push_back(t);
@@ -560,6 +639,11 @@ csw_status csw_swap_out_done(csw_mgr* m, csw_ticket* t, int* done) {
   if (!m || !t || !done) return CSW_ERR_ARG;
   std::lock_guard<std::mutex> lk(m->mu);
   DeviceGuard g(m->device);
+  pump_raw(m);
+  if (t->queued) {  // its copy has not even been issued
+    *done = 0;
+    return CSW_OK;
+  }
   cudaError_t e = cudaEventQuery(t->ev_read);
   if (e != cudaSuccess && e != cudaErrorNotReady) return cuda_fail(e);
   cudaGetLastError();
@@ -573,6 +657,8 @@ csw_status csw_swap_out_sync(csw_mgr* m, csw_ticket* t) {
   {
     std::lock_guard<std::mutex> lk(m->mu);
     if (t->state == T_DEAD) return CSW_ERR_STATE;
+    DeviceGuard g0(m->device);
+    submit_raw_through(m, t);
     ev = t->ev_read;
   }
   DeviceGuard g(m->device);
@@ -584,6 +670,7 @@ csw_status csw_swap_out_wait(csw_mgr* m, csw_ticket* t, csw_stream_t stream) {
   if (!m || !t) return CSW_ERR_ARG;
   std::lock_guard<std::mutex> lk(m->mu);
   DeviceGuard g(m->device);
+  submit_raw_through(m, t);
   cudaError_t e = cudaStreamWaitEvent(stream, t->ev_read, 0);
   return e == cudaSuccess ? CSW_OK : cuda_fail(e);
 }
@@ -691,6 +778,7 @@ csw_status csw_swap_in_start(csw_mgr* m, csw_ticket* t, float* d_dst, csw_stream
   const size_t raw = t->numel * sizeof(float);
   csw_status st = CSW_OK;
   if (t->policy == CSW_POLICY_RAW) {
+    submit_raw_through(m, t);
     e = t->ev_d2h ? cudaStreamWaitEvent(m->s_h2d, t->ev_d2h, 0) : cudaSuccess;
     if (e == cudaSuccess) e = cudaMemcpyAsync(d_dst, t->host, raw, cudaMemcpyHostToDevice, m->s_h2d);
     if (e == cudaSuccess) e = cudaEventRecord(t->ev_done, m->s_h2d);
@@ -732,7 +820,11 @@ csw_status csw_ticket_release(csw_mgr* m, csw_ticket* t) {
   if (t->state == T_DEAD) return CSW_ERR_STATE;
   // Never blocks: memory goes back to the pools now if nothing in flight
   // touches it, otherwise as soon as a later call finds its copies finished.
-  const bool idle = event_done(t->ev_d2h) && event_done(t->ev_h2d) && event_done(t->ev_done);
+  // a raw ticket whose copy has not been issued is never copied at all (taken out of the queue
+  // before anything below can pump it onto the copy stream)
+  const bool never_copied = t->queued;
+  if (never_copied) forget_raw(m, t);
+  const bool idle = never_copied || (event_done(t->ev_d2h) && event_done(t->ev_h2d) && event_done(t->ev_done));
   cudaGetLastError();
   if (idle && t->policy == CSW_POLICY_SPARSE && !t->moved_final) finalize_moved(m, t);
   t->state = T_DEAD;
@@ -814,6 +906,7 @@ csw_status csw_ticket_export(csw_mgr* m, csw_ticket* t, void* dst, size_t cap, s
   std::lock_guard<std::mutex> lk(m->mu);
   DeviceGuard g(m->device);
   if (t->state == T_DEAD) return CSW_ERR_STATE;
+  submit_raw_through(m, t);
   if (t->ev_d2h) {
     cudaError_t e = cudaEventSynchronize(t->ev_d2h);
     if (e != cudaSuccess) return cuda_fail(e);
@@ -892,6 +985,7 @@ csw_status csw_mgr_sync(csw_mgr* m) {
   if (!m) return CSW_ERR_ARG;
   std::lock_guard<std::mutex> lk(m->mu);
   DeviceGuard g(m->device);
+  if (!m->raw_queue.empty()) submit_raw_through(m, m->raw_queue.back());
   cudaError_t e = cudaStreamSynchronize(m->s_codec);
   if (e == cudaSuccess) e = cudaStreamSynchronize(m->s_d2h);
   if (e == cudaSuccess) e = cudaStreamSynchronize(m->s_h2d);

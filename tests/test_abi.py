@@ -77,10 +77,15 @@ def test_cost_decision_is_pure_host_logic(L):
     all_raw = [cs.TensorDesc(t.numel, -1.0, False, t.ready_s, t.need_s) for t in tensors]
     pol_raw, stall_raw = cm.decide(all_raw, fwd)
     assert pol_raw == [2] * 6 and sum(stall) < 0.75 * sum(stall_raw)
-    # when the link keeps up with compute nothing stalls and nothing is compressed
+    # when the link keeps up with compute nothing stalls either way, and the tie goes to the smaller
+    # payload (it leaves the link and the copy engine's queue to others): sparse at 90 % zeros, ZFP
+    # where only loss helps, raw where nothing may be coded
     small = [cs.TensorDesc(1 << 18, 0.9, True, ready_s=1e-4 * i, need_s=1e-3 * (5 - i)) for i in range(5)]
     pol2, stall2 = cm.decide(small, 1e-3)
-    assert pol2 == [2] * 5 and sum(stall2) == 0.0
+    assert pol2 == [3] * 5 and sum(stall2) == 0.0
+    dense = [cs.TensorDesc(1 << 18, 0.0, i % 2 == 0, ready_s=1e-4 * i, need_s=1e-3 * (5 - i)) for i in range(5)]
+    pol3, stall3 = cm.decide(dense, 1e-3)
+    assert pol3 == [6, 2, 6, 2, 6] and sum(stall3) == 0.0
     assert cm.decide([], 0.0) == ([], [])
     # the prediction for a given table: keeping everything costs nothing, and raw tensors that backward
     # wants before they have left are taken back (which is why all-raw can be predicted cheaper than a
