@@ -110,6 +110,7 @@ SIGNATURES = {
     "csw_mgr_destroy": (_I, [_P]),
     "csw_mgr_set_zfp_maxbits": (_I, [_P, _U]),
     "csw_mgr_keep_staged": (_I, [_P, C.c_int]),
+    "csw_swap_out_cancel": (_I, [_P, _P, C.POINTER(C.c_int)]),
     "csw_mgr_get_streams": (_I, [_P, C.POINTER(_P), C.POINTER(_P), C.POINTER(_P)]),
     "csw_swap_out": (_I, [_P, _P, _SZ, _I, _P, C.POINTER(_P)]),
     "csw_swap_out_done": (_I, [_P, _P, C.POINTER(_I)]),

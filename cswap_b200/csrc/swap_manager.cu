@@ -835,6 +835,21 @@ csw_status csw_ticket_release(csw_mgr* m, csw_ticket* t) {
   return CSW_OK;
 }
 
+csw_status csw_swap_out_cancel(csw_mgr* m, csw_ticket* t, int* cancelled) {
+  if (!m || !t || !cancelled) return CSW_ERR_ARG;
+  std::lock_guard<std::mutex> lk(m->mu);
+  DeviceGuard g(m->device);
+  if (t->state == T_DEAD) return CSW_ERR_STATE;
+  *cancelled = t->queued ? 1 : 0;
+  if (t->queued) {
+    forget_raw(m, t);
+    t->state = T_DEAD;
+    drop_from_live(m, t);
+    destroy_ticket(m, t);
+  }
+  return CSW_OK;
+}
+
 csw_status csw_ticket_query(csw_mgr* m, csw_ticket* t, csw_ticket_info* info) {
   if (!m || !t || !info) return CSW_ERR_ARG;
   std::lock_guard<std::mutex> lk(m->mu);

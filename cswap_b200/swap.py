@@ -72,6 +72,8 @@ class Ticket:
             for i, (tk, t) in enumerate(mgr._reading):
                 if tk is self:
                     del mgr._reading[i]
+                    if mgr._cancel(self):       # its copy was never handed to the copy stream
+                        return
                     if not mgr.out_done(self):
                         mgr._retiring.append((_Parked(self._h, self.policy), t))
                         self._h = None
@@ -170,7 +172,8 @@ class SwapManager:
                 if self.out_done(ticket):
                     return None
                 del self._reading[i]
-                self._retiring.append((ticket, t))
+                if not self._cancel(ticket):    # else: never copied at all, nothing to retire
+                    self._retiring.append((ticket, t))
                 self.reclaimed_tensors += 1
                 return t
         return None
@@ -224,6 +227,16 @@ class SwapManager:
         numel = info["numel"]
         return Ticket(self, h.value, tuple(shape) if shape is not None else (numel,), numel, self.device,
                       info["policy"])
+
+    def _cancel(self, ticket) -> bool:
+        """Raw copies out are handed to the copy stream a few at a time; a
+        ticket whose copy is still waiting is dropped without ever being
+        copied (its handle is dead afterwards)."""
+        c = C.c_int()
+        check(lib().csw_swap_out_cancel(self._h, ticket._h, C.byref(c)), "csw_swap_out_cancel")
+        if c.value:
+            ticket._h = None
+        return bool(c.value)
 
     def out_done(self, ticket: Ticket) -> bool:
         d = C.c_int()

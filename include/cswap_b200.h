@@ -240,6 +240,11 @@ csw_status csw_swap_in_wait(csw_mgr* m, csw_ticket* t, csw_stream_t compute);
  * pools at once if no copy is in flight, else when a later call on the manager
  * finds them finished.  The handle is invalid afterwards. */
 csw_status csw_ticket_release(csw_mgr* m, csw_ticket* t);
+/* Raw copies out are handed to the copy stream a few at a time.  If this ticket's copy has
+ * not been handed over yet it never will be: the ticket is released (the handle is dead
+ * afterwards), *cancelled is 1 and the tensor it would have read is free to go at once.
+ * Otherwise nothing happens and *cancelled is 0. */
+csw_status csw_swap_out_cancel(csw_mgr* m, csw_ticket* t, int* cancelled);
 
 typedef struct {
   int policy;            /* policy actually applied                       */
