@@ -596,6 +596,7 @@ class Execution {
       csw_swap_out_done(mgr_, s.ticket, &done);
       if (!done) {
         s.storage->set_data_ptr_noswap(std::move(s.reading));
+        s.reading.clear();  // a moved-from DataPtr keeps its raw pointer: make "no block held" visible
         settle(s);
         reclaimed++;
         poll();
@@ -608,6 +609,7 @@ class Execution {
       // copy and decode were started when the tensor swapped out after this one came back
       check(csw_swap_in_wait(mgr_, s.ticket, stream), "csw_swap_in_wait");
       s.storage->set_data_ptr_noswap(std::move(s.ahead));
+      s.ahead.clear();
     } else {
       at::DataPtr dp = alloc->allocate(s.nbytes);
       check(csw_swap_in(mgr_, s.ticket, static_cast<float*>(dp.get()), stream), "csw_swap_in");
