@@ -48,8 +48,11 @@ def test_cpp_vgg16_step_bench_line():
     d = json.loads(r.stdout.strip().splitlines()[-1])
     rows = d["rows"]
     assert {"no_swap", "raw_swap", "reference_split_zfp8", "zfp8_everywhere", "self_tuned"} <= set(rows)
-    assert rows["no_swap"]["link_bytes_out"] == 0 and rows["raw_swap"]["link_bytes_out"] > 1e8
-    assert rows["zfp8_everywhere"]["link_bytes_out"] < 0.3 * rows["raw_swap"]["link_bytes_out"]
+    # raw copies of tensors that are taken back while they wait in the manager's queue are never made
+    raw = rows["raw_swap"]
+    assert rows["no_swap"]["link_bytes_out"] == 0 and 0 < raw["link_bytes_out"] <= raw["activation_bytes_swapped"]
+    assert raw["activation_bytes_swapped"] > 2.5e8
+    assert rows["zfp8_everywhere"]["link_bytes_out"] < 0.3 * raw["activation_bytes_swapped"]
     # a restored activation is freed as soon as its backward has used it: swapping lowers the peak
     assert rows["zfp8_everywhere"]["peak_device_mib"] < 0.9 * rows["no_swap"]["peak_device_mib"]
     h = d["hidden_activation_bytes"]
