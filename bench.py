@@ -786,7 +786,7 @@ def main():
     name, t_k = ("zfp_encode_slab_kernel", t_enc) if t_enc >= t_dec else ("zfp_decode_slab_kernel", t_dec)
     # DRAM read + write bytes of one launch, from an ncu capture of this exact workload
     # (256 MiB tensor, rate 8); unknown for other sizes / rates
-    ncu_traffic = {("zfp_encode_slab_kernel", 256, 8): 317.9e6, ("zfp_decode_slab_kernel", 256, 8): 275.8e6}
+    ncu_traffic = {("zfp_encode_slab_kernel", 256, 8): 320.7e6, ("zfp_decode_slab_kernel", 256, 8): 276.4e6}
     roofline = {"bound": "hbm", "kernel": name, "achieved": alg / t_k / 1e9, "peak": peak, "unit": "GB/s",
                 "frac": alg / t_k / 1e9 / peak, "peak_kind": f"of {peak_kind}", "traffic": ncu_traffic.get((name, args.mib, args.rate)),
                 "algorithmic_bytes_per_launch": alg,
