@@ -549,3 +549,28 @@ def test_staged_payload_kept_until_the_pool_needs_room(cs):
     assert m.stats()["moved_bytes_in"] == 4 << 20
     tk.release()
     m.close()
+
+
+def test_raw_copies_wait_in_the_managers_queue(cs):
+    """Raw copies out are handed to the copy stream two at a time; a ticket
+    given up while its copy still waits is never copied (csw_swap_out_cancel),
+    and one that is not given up comes back bit for bit."""
+    import torch
+    m = cs.SwapManager(pinned_bytes=512 << 20, staging_bytes=16 << 20)
+    ts = [torch.randn(1 << 20, device="cuda") for _ in range(8)]    # 4 MiB each
+    torch.cuda.synchronize()
+    torch.cuda._sleep(int(4e8))          # the GPU is busy: no copy can start yet (it waits for this stream)
+    tks = [m.swap_out(t, cs.POLICY_RAW) for t in ts]
+    assert not any(m.out_done(tk) for tk in tks)
+    cancelled = sum(m._cancel(tk) for tk in reversed(tks))
+    assert cancelled == 6                # two had been handed to the copy stream already
+    assert [tk.alive for tk in tks] == [True, True] + [False] * 6
+    back = m.swap_in(tks[0])
+    torch.cuda.synchronize()
+    assert torch.equal(back, ts[0])
+    for tk in tks[:2]:
+        tk.release()
+    m.sync()
+    s = m.stats()
+    assert s["moved_bytes_out"] == 2 * (4 << 20) and s["pinned_in_use"] == 0
+    m.close()
